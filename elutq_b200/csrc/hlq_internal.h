@@ -1,0 +1,57 @@
+// Internal declarations shared by the translation units of libhlq_b200.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hlq_b200.h"
+#include "hlq_layout.h"
+
+struct hlq_weight {
+    int device = 0;
+    int n = 0, k = 0, g = 0, q = 0;  // this shard
+    int n_full = 0, k_full = 0;
+    int tp_rank = 0, tp_size = 1, shard_mode = 0;
+    int layout = HLQ_LAYOUT_STREAM;
+    // HLQ_LAYOUT_STREAM: planes = streaming cells, meta = streaming scales/zeros.
+    // HLQ_LAYOUT_EXPORT: planes = uint8 [q][n][k/8]; meta = fp16 scales [q][n][k/g]
+    //                    followed by fp16 zeros [n][k/g].
+    uint8_t *d_planes = nullptr;
+    uint16_t *d_meta = nullptr;
+    uint16_t *d_bias = nullptr;
+    int64_t planes_bytes = 0, meta_bytes = 0;
+};
+
+namespace hlq {
+
+// Records a failing CUDA call for hlq_last_cuda_error(); returns HLQ_ERR_CUDA or HLQ_OK.
+int note_cuda(cudaError_t e);
+void count_launch(int n = 1);
+
+#define HLQ_CUDA(call)                                  \
+    do {                                                \
+        cudaError_t e__ = (call);                       \
+        if (e__ != cudaSuccess) return hlq::note_cuda(e__); \
+    } while (0)
+
+// Workspace layout: [0, 256) header (int status at 0), then counters, then partial sums.
+constexpr size_t kWsHeader = 256;
+constexpr int kLutMaxM = 16;  // rows of x one LUT-GEMV launch handles
+
+struct Workspace {
+    int *status;
+    unsigned *counters;  // [m][blocks]
+    float *partial;      // [m][slices][np]
+};
+size_t workspace_bytes_for(int m, const StreamDims &d);
+Workspace carve_workspace(void *base, int m, const StreamDims &d);
+
+// Kernels' launchers (defined in the .cu files).  All return an hlq_status.
+int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
+                     void *workspace, size_t workspace_bytes, cudaStream_t stream);
+int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
+                     cudaStream_t stream);
+int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, void *y,
+                        int y_dtype, void *workspace, size_t workspace_bytes,
+                        cudaStream_t stream);
+
+}  // namespace hlq

@@ -1,0 +1,210 @@
+"""The exported on-disk format of one quantized linear, and bit-plane packing.
+
+Layout written by the reference's exporter (GPTQ/HLQ.py:177-236) and read by its
+loader (C++/ops/src/arm/parameters.cpp:5-70), per linear directory:
+
+    w_quant.bin          uint8 [q][N][K/8]   bit j of byte i = plane bit of channel 8i+j
+    w_scale.bin          fp16  [q][N][K/g]
+    w_zero.bin           fp16  [N][K/g]
+    bias.bin (optional)  fp16  [N]
+    weight_config.json   weight_data_len, base_bit, use_sparse, in_channel, out_channel,
+                         has_bias (+ groupsize, which the reference's loader reads but its
+                         exporter does not write)
+
+Packing goes through the C ABI (hlq_pack_bits / hlq_unpack_bits); there is no NumPy
+re-implementation here.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+from . import _lib
+
+
+@dataclass
+class ExportedLinear:
+    """The arrays of one exported linear, as NumPy views of the files' bytes."""
+    w_quant: np.ndarray            # uint8 [q, N, K/8]
+    w_scale: np.ndarray            # fp16  [q, N, K/g]
+    w_zero: np.ndarray             # fp16  [N, K/g]
+    bias: Optional[np.ndarray]     # fp16  [N] or None
+    groupsize: int
+
+    @property
+    def bits(self) -> int:
+        return self.w_quant.shape[0]
+
+    @property
+    def out_channel(self) -> int:
+        return self.w_quant.shape[1]
+
+    @property
+    def in_channel(self) -> int:
+        return self.w_quant.shape[2] * 8
+
+    def algorithmic_bytes(self) -> int:
+        return self.w_quant.nbytes + self.w_scale.nbytes + self.w_zero.nbytes
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data
+
+
+def pack_bits(bits: np.ndarray) -> np.ndarray:
+    """uint8 [q, N, K] of {0,1} -> uint8 [q, N, K/8] (GPTQ/HLQ.py:239-251)."""
+    bits = np.ascontiguousarray(bits, dtype=np.uint8)
+    if bits.ndim != 3:
+        raise ValueError("bits must be [q, N, K]")
+    q, n, k = bits.shape
+    if k % 8:
+        raise ValueError("K must be a multiple of 8")
+    out = np.empty((q, n, k // 8), np.uint8)
+    _lib.check(_lib.lib().hlq_pack_bits(_ptr(bits), _ptr(out), q, n, k), "hlq_pack_bits")
+    return out
+
+
+def unpack_bits(packed: np.ndarray) -> np.ndarray:
+    """uint8 [q, N, K/8] -> uint8 [q, N, K] of {0,1}."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    if packed.ndim != 3:
+        raise ValueError("packed must be [q, N, K/8]")
+    q, n, kb = packed.shape
+    out = np.empty((q, n, kb * 8), np.uint8)
+    _lib.check(_lib.lib().hlq_unpack_bits(_ptr(packed), _ptr(out), q, n, kb * 8), "hlq_unpack_bits")
+    return out
+
+
+def export_from_tensors(quantized_w, w_scale, w_zero, bias=None, groupsize: Optional[int] = None
+                        ) -> ExportedLinear:
+    """The tensors ``HLQ.export`` receives -> exported arrays (GPTQ/HLQ.py:207-236).
+
+    quantized_w [N, K, q] of {0,1}; w_scale [N, G, q]; w_zero [N, G, 1]; bias [N] or None.
+    Scales and zeros are rounded to fp16, scales and planes become plane-major.
+    """
+    qw = np.asarray(quantized_w)
+    ws = np.asarray(w_scale, dtype=np.float32)
+    wz = np.asarray(w_zero, dtype=np.float32)
+    if qw.ndim != 3 or ws.ndim != 3 or wz.ndim != 3:
+        raise ValueError("quantized_w, w_scale and w_zero must be 3-D")
+    n, k, q = qw.shape
+    g = groupsize or k // ws.shape[1]
+    if ws.shape != (n, k // g, q) or wz.shape != (n, k // g, 1):
+        raise ValueError("scale/zero shapes do not match [N, K/g, q] / [N, K/g, 1]")
+    planes = np.ascontiguousarray(qw.astype(np.uint8).transpose(2, 0, 1))
+    return ExportedLinear(
+        w_quant=pack_bits(planes),
+        w_scale=np.ascontiguousarray(ws.astype(np.float16).transpose(2, 0, 1)),
+        w_zero=np.ascontiguousarray(wz.astype(np.float16)[:, :, 0]),
+        bias=None if bias is None else np.ascontiguousarray(np.asarray(bias, dtype=np.float32).astype(np.float16)),
+        groupsize=g,
+    )
+
+
+def write_export_dir(path: str, lin: ExportedLinear, write_groupsize: bool = False) -> None:
+    """Write one linear directory exactly as the reference's exporter does.
+
+    ``write_groupsize`` adds the ``groupsize`` key the reference's C++ loader looks for
+    (parameters.cpp:17) but its exporter omits.
+    """
+    os.makedirs(path, exist_ok=True)
+    lin.w_zero.astype(np.float16).tofile(os.path.join(path, "w_zero.bin"))
+    lin.w_scale.astype(np.float16).tofile(os.path.join(path, "w_scale.bin"))
+    lin.w_quant.astype(np.uint8).tofile(os.path.join(path, "w_quant.bin"))
+    cfg = {
+        "weight_data_len": int(lin.in_channel * lin.out_channel * lin.bits / 8),
+        "base_bit": int(lin.bits),
+        "use_sparse": False,
+        "in_channel": int(lin.in_channel),
+        "out_channel": int(lin.out_channel),
+        "has_bias": lin.bias is not None,
+    }
+    if lin.bias is not None:
+        lin.bias.astype(np.float16).tofile(os.path.join(path, "bias.bin"))
+    if write_groupsize:
+        cfg["groupsize"] = int(lin.groupsize)
+    with open(os.path.join(path, "weight_config.json"), "w") as f:
+        json.dump(cfg, f, indent=4)
+
+
+def read_export_dir(path: str) -> ExportedLinear:
+    """Read one linear directory (parameters.cpp:11-57).
+
+    Errors follow the reference's loader where it has any: a missing or invalid
+    ``weight_config.json`` raises (fileutils.cpp:32-43).  Unlike the reference, short
+    reads raise too instead of being ignored (parameters.cpp:38), and sparse exports are
+    rejected.  The group size is taken from the config when present, else derived from
+    the size of ``w_zero.bin``.
+    """
+    cfg_path = os.path.join(path, "weight_config.json")
+    if not os.path.exists(cfg_path):
+        raise RuntimeError(f"File is not exists: {cfg_path}")
+    with open(cfg_path) as f:
+        try:
+            cfg = json.load(f)
+        except json.JSONDecodeError as e:
+            raise RuntimeError(f"Invalid json file: {cfg_path}") from e
+    if cfg.get("use_sparse", False):
+        raise NotImplementedError("sparse extra-bit planes are not supported")
+    q = int(cfg["base_bit"])
+    k = int(cfg["in_channel"])
+    n = int(cfg["out_channel"])
+    if q < 1 or q > 4 or k % 8 or n <= 0:
+        raise ValueError(f"unsupported weight_config: bits={q} in={k} out={n}")
+    want = int(cfg.get("weight_data_len", n * k * q // 8))
+    if want != n * k * q // 8:
+        raise ValueError("weight_data_len does not match in_channel*out_channel*base_bit/8")
+    w_quant = np.fromfile(os.path.join(path, "w_quant.bin"), dtype=np.uint8)
+    if w_quant.size != want:
+        raise ValueError(f"w_quant.bin holds {w_quant.size} bytes, expected {want}")
+    w_zero = np.fromfile(os.path.join(path, "w_zero.bin"), dtype=np.float16)
+    g = int(cfg.get("groupsize", 0) or 0)
+    if g <= 0:
+        if w_zero.size == 0 or (n * k) % w_zero.size:
+            raise ValueError("cannot derive the group size from w_zero.bin")
+        g = n * k // w_zero.size
+    if k % g or g % 8 or w_zero.size != n * k // g:
+        raise ValueError(f"w_zero.bin holds {w_zero.size} values, expected {n * k // g} at g={g}")
+    w_scale = np.fromfile(os.path.join(path, "w_scale.bin"), dtype=np.float16)
+    if w_scale.size != q * n * k // g:
+        raise ValueError(f"w_scale.bin holds {w_scale.size} values, expected {q * n * k // g}")
+    bias = None
+    if cfg.get("has_bias", False):
+        bias = np.fromfile(os.path.join(path, "bias.bin"), dtype=np.float16)
+        if bias.size != n:
+            raise ValueError(f"bias.bin holds {bias.size} values, expected {n}")
+    return ExportedLinear(w_quant.reshape(q, n, k // 8), w_scale.reshape(q, n, k // g),
+                          w_zero.reshape(n, k // g), bias, g)
+
+
+def repack_host(lin: ExportedLinear):
+    """Exported arrays -> (planes, meta) of the streaming layout, on the CPU."""
+    L = _lib.lib()
+    pb, mb = _lib.c_int64(), _lib.c_int64()
+    n, k, g, q = lin.out_channel, lin.in_channel, lin.groupsize, lin.bits
+    _lib.check(L.hlq_stream_sizes(n, k, g, q, pb, mb), "hlq_stream_sizes")
+    planes = np.empty(pb.value, np.uint8)
+    meta = np.empty(mb.value // 2, np.uint16)
+    wq = np.ascontiguousarray(lin.w_quant)
+    ws = np.ascontiguousarray(lin.w_scale).view(np.uint16)
+    wz = np.ascontiguousarray(lin.w_zero).view(np.uint16)
+    _lib.check(L.hlq_repack_host(_ptr(wq), _ptr(ws), _ptr(wz), n, k, g, q, _ptr(planes), _ptr(meta)),
+               "hlq_repack_host")
+    return planes, meta
+
+
+def unrepack_host(planes: np.ndarray, meta: np.ndarray, n: int, k: int, g: int, q: int) -> ExportedLinear:
+    """Inverse of :func:`repack_host`."""
+    L = _lib.lib()
+    wq = np.empty((q, n, k // 8), np.uint8)
+    ws = np.empty((q, n, k // g), np.uint16)
+    wz = np.empty((n, k // g), np.uint16)
+    planes = np.ascontiguousarray(planes, dtype=np.uint8)
+    meta = np.ascontiguousarray(meta, dtype=np.uint16)
+    _lib.check(L.hlq_unrepack_host(_ptr(planes), _ptr(meta), n, k, g, q, _ptr(wq), _ptr(ws), _ptr(wz)),
+               "hlq_unrepack_host")
+    return ExportedLinear(wq, ws.view(np.float16), wz.view(np.float16), None, g)

@@ -1,0 +1,200 @@
+/*
+ * hlq_b200 -- C ABI of the B200 (sm_100a) implementation of ELUTQ's quantized-linear path.
+ *
+ * HLQ (Hierarchical Linear Quantization): each group of g input channels of one output
+ * row is stored as q binary bit-planes b_i in {0,1}, one fp16 scale alpha_i per plane and
+ * one fp16 offset z, so that  w = sum_i alpha_i * b_i + z.
+ *
+ * The entry points mirror the reference's operator interface for this path; each
+ * declaration names the reference interface it replaces (paths relative to the ELUTQ
+ * project root).  The reference has no FFI layer: its interface is a direct C++ call
+ * (arm_gemm + weight_tensor + load_Parameter) and the on-disk export format.
+ *
+ * Conventions
+ *  - every function returns an hlq_status (0 = HLQ_OK); nothing exits or throws;
+ *  - pointers named d_* are device pointers, h_* host pointers; plain names accept either
+ *    where the comment says so;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *    device work is enqueued on it and the call returns without synchronizing unless the
+ *    comment says otherwise;
+ *  - tensors are row-major; activations x are [m, k], outputs y are [m, n].
+ */
+#ifndef HLQ_B200_H
+#define HLQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum hlq_status {
+    HLQ_OK = 0,
+    HLQ_ERR_INVALID_ARGUMENT = 1, /* null pointer, bad enum value, negative size            */
+    HLQ_ERR_SHAPE = 2,            /* k % g, k % 8, g % 8, bits outside 1..4, bad shard split */
+    HLQ_ERR_WORKSPACE = 3,        /* workspace missing or smaller than hlq_workspace_bytes   */
+    HLQ_ERR_CUDA = 4,             /* a CUDA runtime call failed (see hlq_last_cuda_error)    */
+    HLQ_ERR_NO_DEVICE = 5,        /* no CUDA device / wrong architecture (needs sm_100)      */
+    HLQ_ERR_UNSUPPORTED = 6,      /* combination not implemented (e.g. dtype)                */
+    HLQ_ERR_ALIGNMENT = 7,        /* pointer not aligned as documented                       */
+    HLQ_ERR_KERNEL = 8            /* a kernel reported a failure through its status word     */
+} hlq_status;
+
+typedef enum hlq_dtype { HLQ_F16 = 0, HLQ_BF16 = 1, HLQ_F32 = 2 } hlq_dtype;
+
+/* How a weight is cut for tensor parallelism when it is loaded. */
+typedef enum hlq_shard_mode {
+    HLQ_SHARD_NONE = 0,
+    HLQ_SHARD_ROWS = 1, /* column-parallel: output rows n are split; no collective needed    */
+    HLQ_SHARD_COLS = 2  /* row-parallel: input channels k are split (whole groups, multiples */
+                        /* of 128 channels); outputs of the ranks must be summed             */
+} hlq_shard_mode;
+
+/* Device-side storage of a loaded weight. */
+typedef enum hlq_layout {
+    HLQ_LAYOUT_STREAM = 0, /* slice/oct streaming layout of the LUT GEMV (g in 32, 64, 128) */
+    HLQ_LAYOUT_EXPORT = 1  /* the exported arrays kept as they are (any g % 8 == 0)          */
+} hlq_layout;
+
+/* Flags of hlq_weight_from_export. */
+#define HLQ_FLAG_FORCE_EXPORT_LAYOUT 1u /* keep the exported arrays; use the generic kernel */
+
+/* Opaque handle that owns the device buffers of one quantized linear.
+ * Replaces: class weight_tensor, C++/ops/include/arm/arm_nnstructures.h:11-37. */
+typedef struct hlq_weight hlq_weight;
+
+typedef struct hlq_weight_info {
+    int in_channel;      /* k of this shard                       */
+    int out_channel;     /* n of this shard                       */
+    int groupsize;       /* g                                     */
+    int bits;            /* q                                     */
+    int has_bias;
+    int layout;          /* hlq_layout                            */
+    int device;
+    int tp_rank, tp_size, shard_mode;
+    int full_in_channel, full_out_channel; /* before sharding     */
+    int64_t device_bytes;    /* bytes this handle holds on the device              */
+    int64_t algorithmic_bytes; /* q*n*k/8 + 2*(q+1)*n*k/g: planes + fp16 scales + fp16 zeros */
+} hlq_weight_info;
+
+/* ---- bit-plane packing -------------------------------------------------------------- */
+
+/* bits: uint8 [q][n][k] of 0/1  ->  packed: uint8 [q][n][k/8]; channel 8i+j goes to bit j
+ * of byte i (bit 0 = lowest channel).  Host buffers, runs on the calling thread.
+ * Replaces: HLQ.Pack_T_MAC_Weight, GPTQ/HLQ.py:239-251. */
+int hlq_pack_bits(const uint8_t *h_bits, uint8_t *h_packed, int q, int64_t n, int64_t k);
+/* Inverse of hlq_pack_bits (the reference has no unpacker; this is the exact inverse of
+ * GPTQ/HLQ.py:239-251). */
+int hlq_unpack_bits(const uint8_t *h_packed, uint8_t *h_bits, int q, int64_t n, int64_t k);
+/* The same two operations on device buffers, as CUDA kernels on `stream`. */
+int hlq_pack_bits_device(const uint8_t *d_bits, uint8_t *d_packed, int q, int64_t n, int64_t k,
+                         void *stream);
+int hlq_unpack_bits_device(const uint8_t *d_packed, uint8_t *d_bits, int q, int64_t n,
+                           int64_t k, void *stream);
+
+/* ---- streaming layout (load-time re-layout) ----------------------------------------- */
+
+/* Sizes, in bytes, of the streaming-layout buffers of an [n, k] weight.
+ * Replaces the size arithmetic of load_Parameter, C++/ops/src/arm/parameters.cpp:34-50. */
+int hlq_stream_sizes(int n, int k, int groupsize, int bits, int64_t *planes_bytes,
+                     int64_t *meta_bytes);
+/* Exported arrays -> streaming layout, on the host (reference implementation of the
+ * layout, also usable to prepare buffers off-line).  w_quant uint8 [q][n][k/8], w_scale
+ * fp16 [q][n][k/g], w_zero fp16 [n][k/g].
+ * Replaces: t_mac_g4_rearrange_weight_normal_impl, C++/ops/src/arm/arm_t_mac_kernal.cpp:472-552. */
+int hlq_repack_host(const uint8_t *h_w_quant, const uint16_t *h_w_scale,
+                    const uint16_t *h_w_zero, int n, int k, int groupsize, int bits,
+                    uint8_t *h_planes, uint16_t *h_meta);
+/* Exact inverse of hlq_repack_host. */
+int hlq_unrepack_host(const uint8_t *h_planes, const uint16_t *h_meta, int n, int k,
+                      int groupsize, int bits, uint8_t *h_w_quant, uint16_t *h_w_scale,
+                      uint16_t *h_w_zero);
+/* The same as CUDA kernels on device buffers. */
+int hlq_repack_device(const uint8_t *d_w_quant, const uint16_t *d_w_scale,
+                      const uint16_t *d_w_zero, int n, int k, int groupsize, int bits,
+                      uint8_t *d_planes, uint16_t *d_meta, void *stream);
+int hlq_unrepack_device(const uint8_t *d_planes, const uint16_t *d_meta, int n, int k,
+                        int groupsize, int bits, uint8_t *d_w_quant, uint16_t *d_w_scale,
+                        uint16_t *d_w_zero, void *stream);
+
+/* ---- weights ------------------------------------------------------------------------ */
+
+/* Build a device-resident weight from the exported arrays of ONE linear:
+ *   w_quant uint8 [bits][out_ch][in_ch/8], w_scale fp16 [bits][out_ch][in_ch/g],
+ *   w_zero fp16 [out_ch][in_ch/g], bias fp16 [out_ch] or NULL.
+ * The four pointers may be host or device pointers (detected).  in_ch/out_ch are the FULL
+ * sizes; with tp_size > 1 only the shard of tp_rank is uploaded and kept (shard_mode
+ * says how; with HLQ_SHARD_COLS the bias is kept by rank 0 only).  The call selects
+ * `device`, synchronizes `stream` before returning, and the handle owns its buffers.
+ * Replaces: load_Parameter(PARAM_TYPE_LINEAR), C++/ops/src/arm/parameters.cpp:5-70, and
+ * the re-layout it calls (arm_t_mac_kernal.cpp:652-674). */
+int hlq_weight_from_export(hlq_weight **out, const void *w_quant, const void *w_scale,
+                           const void *w_zero, const void *bias_or_null, int in_ch, int out_ch,
+                           int groupsize, int bits, int device, int tp_rank, int tp_size,
+                           int shard_mode, unsigned flags, void *stream);
+/* Write this handle's shard back as exported arrays into HOST buffers sized for the shard
+ * (bias may be NULL).  Synchronizes.  Bit-exact inverse of hlq_weight_from_export. */
+int hlq_weight_to_export(const hlq_weight *w, void *h_w_quant, void *h_w_scale, void *h_w_zero,
+                         void *h_bias_or_null, void *stream);
+/* Replaces: ~weight_tensor, C++/ops/include/arm/arm_nnstructures.h:30-36. */
+int hlq_weight_free(hlq_weight *w);
+int hlq_weight_get_info(const hlq_weight *w, hlq_weight_info *info);
+/* Device pointers of the handle's buffers (NULL where the layout has none): the packed
+ * planes, the scales/zeros, and the bias.  For benchmarks that fill weights on the device. */
+int hlq_weight_buffers(const hlq_weight *w, void **d_planes, int64_t *planes_bytes,
+                       void **d_meta, int64_t *meta_bytes, void **d_bias);
+/* Allocate a weight of the given (unsharded) shape with undefined contents, to be filled
+ * through hlq_weight_buffers.  No counterpart in the reference (benchmark helper). */
+int hlq_weight_alloc(hlq_weight **out, int in_ch, int out_ch, int groupsize, int bits,
+                     int has_bias, int device, unsigned flags);
+
+/* ---- forward ------------------------------------------------------------------------ */
+
+/* Bytes of device scratch hlq_linear_forward needs for this problem (0 is possible).
+ * Replaces the temp_workplace sizing of C++/ops/src/arm/arm_gemm.cpp:333-334,348. */
+size_t hlq_workspace_bytes(int m, int k, int n, int bits, int groupsize);
+/* Zero a freshly allocated workspace once, before its first use (the forward kernels
+ * leave it in the state they need).  One workspace serves one stream at a time. */
+int hlq_workspace_init(void *d_workspace, size_t bytes, void *stream);
+
+/* Read the status word the kernels of the last launches left in the workspace
+ * (synchronizes `stream`).  Returns HLQ_ERR_KERNEL and a non-zero *kernel_status when a
+ * kernel gave up on a bounded wait (1) or found its shared-memory window unusable (2).
+ * No counterpart in the reference, whose CPU kernel has no asynchronous failures. */
+int hlq_workspace_status(const void *d_workspace, void *stream, int *kernel_status);
+
+/* y[m, n] = x[m, k] . W_hat^T + bias, W_hat = sum_i alpha_i b_i + z; y is overwritten.
+ * x and y are device pointers with row strides k and n; x_dtype in {F16, BF16}, y_dtype in
+ * {F16, BF16, F32}; accumulation is fp32.  k and n must equal the handle's shard sizes.
+ * With HLQ_SHARD_COLS the result is this rank's partial sum.  Not re-entrant on one
+ * workspace.  x and y must be 16-byte aligned.
+ * Replaces: arm_gemm, C++/ops/include/arm/arm_gemm.h:4-14 (dispatch at
+ * C++/ops/src/arm/arm_gemm.cpp:871-924). */
+int hlq_linear_forward(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,
+                       void *d_workspace, size_t workspace_bytes, const hlq_weight *w,
+                       void *stream);
+
+/* Same contract, but forces one implementation: 0 = automatic (what hlq_linear_forward
+ * does), 1 = LUT GEMV on the streaming layout, 2 = generic LUT GEMV on the exported layout,
+ * 3 = dequantize + tensor-core GEMM.  For tests and measurements. */
+int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int x_dtype,
+                            void *d_y, int y_dtype, void *d_workspace, size_t workspace_bytes,
+                            const hlq_weight *w, void *stream);
+
+/* ---- diagnostics -------------------------------------------------------------------- */
+
+/* Human-readable text for an hlq_status.  Replaces the reference's exit(-1)/exceptions
+ * (C++/common/include/Allocate.h:10-13, C++/common/src/fileutils.cpp:32-43). */
+const char *hlq_last_error_string(int status);
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+int hlq_last_cuda_error(void);
+/* Number of kernels this library has launched in this process (all threads). */
+int64_t hlq_kernel_launch_count(void);
+/* ABI version of this header. */
+int hlq_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HLQ_B200_H */
