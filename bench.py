@@ -184,7 +184,9 @@ def workload_config(args, fused):
                         f"{args.layers} layers", "bits": args.bits, "groupsize": args.groupsize,
             "batch": args.batch, "layers": args.layers, "fused_qkv_gate_up": bool(fused),
             "l2": "inputs (2.07 GB of weights per step) larger than L2; no flush needed",
-            "launch": "cuda graph of one step" if not args.no_graph else "stream launches"}
+            "launch": ("cuda graph of one step" if not args.no_graph else "stream launches")
+                      + {"none": ", one launch per projection", "layer": ", one grouped launch per layer",
+                         "model": ", one grouped launch per step"}[args.group]}
 
 
 # ------------------------------------------------------------------------------------------
@@ -240,7 +242,24 @@ def run_gpu(args):
     ws = Workspace(ws_bytes, dev)
     stream = torch.cuda.Stream(device=dev)
 
+    xs = [x_all[xoff[i]:xoff[i + 1]].view(m, k) for i, (n, k) in enumerate(shapes)]
+    ys = [y_all[yoff[i]:yoff[i + 1]].view(m, n) for i, (n, k) in enumerate(shapes)]
+    groups = []
+    if args.group != "none":
+        from elutq_b200.linear import HLQGroup
+        per = len(projection_set(fuse=args.fuse)) if args.group == "layer" else nlin
+        for a0 in range(0, nlin, per):
+            grp = HLQGroup(weights[a0:a0 + per], max_m=m)
+            grp.bind(xs[a0:a0 + per], ys[a0:a0 + per])
+            groups.append(grp)
+
     def one_step(sptr):
+        if groups:
+            for grp in groups:
+                st = L.hlq_group_forward(grp.handle, m, sptr)
+                if st:
+                    _lib.check(st, "hlq_group_forward")
+            return
         for i, (n, k) in enumerate(shapes):
             st = L.hlq_linear_forward(m, k, n, x_all.data_ptr() + 2 * xoff[i], _lib.HLQ_F16,
                                       y_all.data_ptr() + 2 * yoff[i], _lib.HLQ_F16, ws.ptr, ws.nbytes,
@@ -254,7 +273,7 @@ def run_gpu(args):
         one_step(stream.cuda_stream)          # also configures the kernels before any capture
         launches_per_step = L.hlq_kernel_launch_count() - before
         stream.synchronize()
-        assert ws.kernel_status() == 0
+        assert ws.kernel_status() == 0 and all(g_.kernel_status() == 0 for g_ in groups)
         if args.no_graph:
             def step():
                 one_step(stream.cuda_stream)
@@ -301,7 +320,7 @@ def run_gpu(args):
         f1.record(stream)
         barrier()
         ms_e2e = f0.elapsed_time(f1)
-        assert ws.kernel_status() == 0
+        assert ws.kernel_status() == 0 and all(g_.kernel_status() == 0 for g_ in groups)
 
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
@@ -362,6 +381,9 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--fuse", action="store_true", help="load q/k/v and gate/up as one weight each")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host every step")
+    ap.add_argument("--group", default="model", choices=["none", "layer", "model"],
+                    help="run the projections as one persistent launch per layer / per step, "
+                         "or as one launch per projection")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-layers", type=int, default=4)
     ap.add_argument("--cpu-steps", type=int, default=10)

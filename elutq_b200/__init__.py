@@ -19,7 +19,7 @@ __all__ = [
 
 def __getattr__(name):
     # torch-dependent parts are imported on first use
-    if name in ("HLQLinear", "HLQWeight", "Workspace", "linear_forward", "workspace_bytes"):
+    if name in ("HLQLinear", "HLQWeight", "HLQGroup", "Workspace", "linear_forward", "workspace_bytes"):
         from . import linear
         return getattr(linear, name)
     raise AttributeError(name)

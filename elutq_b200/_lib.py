@@ -66,6 +66,12 @@ SIGNATURES = {
                                                  c_size_t, c_void_p, c_void_p]),
     "hlq_linear_forward_impl": (c_int, [c_int] * 4 + [c_void_p, c_int, c_void_p, c_int, c_void_p,
                                                       c_size_t, c_void_p, c_void_p]),
+    "hlq_group_create": (c_int, [POINTER(c_void_p), c_int, POINTER(c_void_p), c_int]),
+    "hlq_group_bind": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_void_p]),
+    "hlq_group_forward": (c_int, [c_void_p, c_int, c_void_p]),
+    "hlq_group_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
+    "hlq_group_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int64), POINTER(c_int64)]),
+    "hlq_group_free": (c_int, [c_void_p]),
     "hlq_last_error_string": (c_char_p, [c_int]),
     "hlq_last_cuda_error": (c_int, []),
     "hlq_kernel_launch_count": (c_int64, []),

@@ -5,26 +5,35 @@
 //   C++/ops/src/arm/arm_t_mac_kernal.cpp:95-138   (16-entry partial-sum table per 4 channels)
 //   C++/ops/src/arm/arm_t_mac_kernal.cpp:364-469  (per-plane table lookups, alpha scaling)
 //
-// lut8_gemv_kernel (streaming layout, see hlq_layout.h)
-//   One CTA per SM walks a contiguous range of (slice, oct) units.  Per slice it
-//     1. copies the 512 activations of the slice into shared memory with one TMA bulk copy,
-//     2. builds, for every 8 activations, the 256-entry fp32 table of subset sums.  Each
-//        table is the sum of the two 16-entry tables of its 4-activation halves, so one
-//        lookup consumes a whole packed byte (two nibbles of the reference's scheme).
-//        The 64 tables of a slice are interleaved so that entry e of every table sits in
-//        the same 256-byte row: address = base + 256*e + offset(table).  With the table
-//        block aligned to 64 KB, the address of a lookup is ONE byte-permute (prmt) that
-//        drops the packed byte into bits 8..15 of a per-lane base register.
-//     3. streams its cells with 128-bit loads (one cell = 8 rows x 512 channels of one
-//        plane; a lane's 16 bytes are one row's 128 channels = one group at g = 128) and
-//        per byte does prmt + ld.shared + fadd.  The byte-pair permutation of the layout
-//        makes the 32 lanes of every lookup hit 32 different banks.
-//     4. scales each plane's group sum by its fp16 alpha, adds z * (sum of the group's
-//        activations), reduces the four lanes of a row with warp shuffles and writes the
-//        row's fp32 partial for this slice.
-//   The last CTA to finish a block of 32 rows (one atomic counter per block) adds the
-//   partials of all slices in slice order, adds the bias and writes y: the result does not
-//   depend on scheduling.
+// lut8_gemv_kernel (streaming layout, see hlq_layout.h) is a persistent kernel: one CTA per
+// SM walks a contiguous range of (job, slice, duo) units, where a job is one linear of a
+// group (or the single linear of hlq_linear_forward), a slice is 512 input channels and a
+// duo is 16 output rows.  A maximal run of units inside one slice of one job is a SEGMENT.
+//
+// Per segment the 16 CONSUMER warps
+//   1. build, for every 8 activations of the slice, the 256-entry fp32 table of subset sums.
+//      Each table is the sum of the two 16-entry tables of its 4-activation halves, so one
+//      lookup consumes a whole packed byte (two nibbles of the reference's scheme).  The 64
+//      tables of a slice are interleaved so that entry e of every table sits in the same
+//      256-byte row: address = base + 256*e + offset(table).  With the table block aligned to
+//      64 KB, the address of a lookup is ONE byte-permute (prmt) that drops the packed byte
+//      into bits 8..15 of a per-lane base register;
+//   2. stream their duos with 128-bit loads through a ring of three register tiles (a lane's
+//      16 bytes are one row's 128 channels = one group at g = 128) and per byte do
+//      prmt + ld.shared + fadd.  The byte-pair permutation of the layout makes the 32 lanes
+//      of every lookup hit 32 different banks;
+//   3. scale each plane's group sum by its fp16 alpha, add z * (sum of the group's
+//      activations), reduce the four lanes of a row with warp shuffles and add the row's
+//      sum for this slice into the row's fp32 accumulator in global memory (red.add.f32);
+//   4. issue the first loads of the NEXT segment before handing this one over.
+// Four FINALIZER warps run beside them: warp 16 walks the unit range one segment ahead,
+// publishes segment descriptors in shared memory and brings each slice's 512 activations in
+// with a TMA bulk copy (double buffered); all four then publish finished segments: one
+// atomic counter per block of 32 rows counts finished (slice, duo) units, and whoever
+// completes a block reads its 32 accumulators, adds the bias, writes y and clears the
+// accumulators and the counter for the next launch.  The consumers never wait for this
+// completion pass.  The slices of a row are added in the order their CTAs finish, so fp32
+// results can differ in the last bit between runs.
 //
 // lut4_gemv_kernel (exported layout, any group size that is a multiple of 8)
 //   The reference's scheme as it stands: a 16-entry table per 4 activations in shared
@@ -33,39 +42,72 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <vector>
 
 #include "hlq_internal.h"
 
 namespace hlq {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = kThreads / 32;
+constexpr int kConsumerWarps = 16;
+constexpr int kFinalWarps = 4;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kFinalizers = kFinalWarps * 32;
+constexpr int kThreads = kConsumers + kFinalizers;
 constexpr uint32_t kTableBytes = 65536;
-constexpr uint32_t kAuxBytes = 8192;   // activations, group sums, mbarrier, completion list
-constexpr int kListCap = 512;
+constexpr uint32_t kAuxBytes = 8192;
 constexpr int kSpinLimit = 1 << 22;
 
-// aux region layout (bytes from its start)
-constexpr uint32_t kAuxX = 0;          // 512 x 16-bit activations (1 KB)
-constexpr uint32_t kAuxXsum = 1024;    // up to 16 group sums (fp32)
-constexpr uint32_t kAuxMbar = 1152;    // one 8-byte mbarrier
-constexpr uint32_t kAuxListN = 1160;   // int: entries in the completion list
-constexpr uint32_t kAuxFlag = 1164;    // int: CTA-wide failure flag
-constexpr uint32_t kAuxList = 2048;    // kListCap ints
+// named barriers (0 is __syncthreads)
+constexpr int kBarConsumers = 1;   // 512 consumer threads
+constexpr int kBarSegDone = 2;     // +slot: consumers arrive, finalizers sync (640)
+constexpr int kBarFinalizers = 6;  // 128 finalizer threads
 
-struct GemvArgs {
+// One linear of a launch.
+struct Job {
     const uint8_t *planes;
     const uint16_t *meta;
-    const void *x;
-    void *y;
     const uint16_t *bias;
-    float *partial;
-    unsigned *counters;
-    int *status;
-    int n, k, np, slices, octs, blocks;
+    float *acc;           // [m][np] fp32 accumulators, zero between launches
+    unsigned *counters;   // [m][blocks]
+    const void *x;        // [m][k]
+    void *y;              // [m][n]
+    int n, k, np, slices, duos, blocks;
     int x_dtype, y_dtype;
-    uint32_t dyn_smem;
+    long long unit_begin; // first (slice, duo) unit of this job in the launch
 };
+
+struct GemvArgs {
+    const Job *jobs;      // njobs descriptors in global memory, or nullptr
+    int njobs;            // 0: use `single`
+    long long total_units;
+    int *status;
+    uint32_t dyn_smem;
+    Job single;
+};
+
+// Descriptor of one segment, written by the control warp into shared memory.
+struct Seg {
+    const uint8_t *planes;  // first cell of the segment
+    const uint16_t *meta;   // first meta entry of the segment
+    const uint16_t *bias;
+    float *acc;             // accumulator row base of mrow
+    unsigned *counters;     // counters of mrow
+    void *y;
+    long long y_base;       // element offset of mrow in y
+    int n, np, slices;
+    int duo_a, duo_b;
+    int x_dtype, y_dtype;
+    int live;
+};
+
+// aux region layout (bytes from its start)
+constexpr uint32_t kAuxX = 0;          // 2 x 512 16-bit activations
+constexpr uint32_t kAuxXsum = 2048;    // up to 16 group sums (fp32)
+constexpr uint32_t kAuxMbarDesc = 2112;  // 2 mbarriers
+constexpr uint32_t kAuxMbarX = 2128;     // 2 mbarriers
+constexpr uint32_t kAuxFlag = 2144;    // int: CTA-wide failure flag
+constexpr uint32_t kAuxSeg = 2304;     // 2 x Seg (<= 128 bytes each)
+static_assert(sizeof(Seg) <= 128, "Seg must fit its slot");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -75,10 +117,10 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
 }
-// the constant offset folds into the instruction's immediate field
-template <int IMM>
-__device__ __forceinline__ float lds_f32_imm(uint32_t addr) {
-    return lds_f32(addr + (uint32_t)IMM);
+__device__ __forceinline__ float lds_f32_hi(uint32_t addr) {   // second bank-row of the table row
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+128];" : "=f"(v) : "r"(addr));
+    return v;
 }
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
@@ -95,6 +137,16 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const void *p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream_v2(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
 __device__ __forceinline__ float ldcg_f32(const float *p) {
@@ -115,7 +167,12 @@ __device__ __forceinline__ void store_y(void *y, int64_t idx, float v, int dtype
 // ---- mbarrier + TMA bulk copy (non-tensor form), all waits bounded -----------------------
 __device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes)
@@ -152,61 +209,59 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+template <int ID, int COUNT>
+__device__ __forceinline__ void named_bar_sync() {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync_dyn(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive_dyn(int id, int count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 
-// ---- per-lane registers of one prefetched group of OU octs -------------------------------
-template <int Q, int GPW, int OU>
+// ---- per-lane registers of one duo (2 octs x Q planes) -----------------------------------
+template <int Q, int GPW>
 struct Tile {
-    uint4 w[OU][Q];
-    uint32_t mt[OU][Q + 1][(GPW + 1) / 2];  // GPW fp16 values per (oct, plane-or-zero)
+    uint4 w[2][Q];
+    uint32_t mt[Q + 1][GPW];  // 2*GPW fp16 values per plane-or-zero: [oct & 1][u]
 };
 
-template <int Q, int GPW, int OU>
-__device__ __forceinline__ void load_tile(Tile<Q, GPW, OU> &t, const GemvArgs &a, int s, int oct0,
-                                          int oct_end, int lane) {
+template <int Q, int GPW>
+__device__ __forceinline__ void load_tile(Tile<Q, GPW> &t, const uint8_t *pl, const uint16_t *mp) {
 #pragma unroll
-    for (int ou = 0; ou < OU; ++ou) {
-        const int oct = oct0 + ou;
-        if (oct < oct_end) {
-            const int64_t cell = (int64_t)s * a.octs + oct;
-            const uint8_t *pp = a.planes + cell * (Q * kCellBytes) + lane * 16;
+    for (int ou = 0; ou < 2; ++ou)
 #pragma unroll
-            for (int p = 0; p < Q; ++p) t.w[ou][p] = ldg_stream_v4(pp + p * kCellBytes);
-            const uint16_t *mp = a.meta + (cell * (Q + 1) * 32 + lane) * GPW;
+        for (int p = 0; p < Q; ++p) t.w[ou][p] = ldg_stream_v4(pl + (ou * Q + p) * kCellBytes);
 #pragma unroll
-            for (int p = 0; p <= Q; ++p) {
-                const uint16_t *m = mp + p * 32 * GPW;
-                if (GPW == 1) {
-                    t.mt[ou][p][0] = __ldg(m);
-                } else if (GPW == 2) {
-                    t.mt[ou][p][0] = __ldg((const uint32_t *)m);
-                } else {
-                    uint2 v = __ldg((const uint2 *)m);
-                    t.mt[ou][p][0] = v.x;
-                    t.mt[ou][p][(GPW + 1) / 2 - 1] = v.y;
-                }
-            }
+    for (int pp = 0; pp <= Q; ++pp) {
+        const uint16_t *m = mp + pp * (32 * 2 * GPW);
+        if (GPW == 1) {
+            t.mt[pp][0] = ldg_stream_u32(m);
+        } else if (GPW == 2) {
+            const uint2 v = ldg_stream_v2(m);
+            t.mt[pp][0] = v.x;
+            t.mt[pp][GPW - 1] = v.y;
         } else {
-#pragma unroll
-            for (int p = 0; p < Q; ++p) t.w[ou][p] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int p = 0; p <= Q; ++p)
-#pragma unroll
-                for (int h = 0; h < (GPW + 1) / 2; ++h) t.mt[ou][p][h] = 0;
+            const uint4 v = ldg_stream_v4(m);
+            t.mt[pp][0] = v.x;
+            t.mt[pp][1 % GPW] = v.y;
+            t.mt[pp][2 % GPW] = v.z;
+            t.mt[pp][3 % GPW] = v.w;
         }
     }
 }
 
+// fp16 value h (h = ou * GPW + u) of a meta entry
 template <int GPW>
-__device__ __forceinline__ float meta_value(const uint32_t (&m)[(GPW + 1) / 2], int u) {
-    const uint32_t word = m[u >> 1];
-    const uint16_t h = (u & 1) ? (uint16_t)(word >> 16) : (uint16_t)(word & 0xffffu);
-    return __half2float(__ushort_as_half(h));
+__device__ __forceinline__ float meta_value(const uint32_t (&m)[GPW], int h) {
+    const uint32_t word = m[h >> 1];
+    return __half2float(__ushort_as_half((h & 1) ? (uint16_t)(word >> 16) : (uint16_t)(word & 0xffffu)));
 }
 
 // 16 lookups of one 128-bit word; sums per positional sub-group (16 / GPW bytes each).
 template <int GPW>
-__device__ __forceinline__ void lookup_word(const uint4 &w, const uint32_t (&rt)[8],
-                                            float (&sum)[GPW]) {
+__device__ __forceinline__ void lookup_word(const uint4 &w, const uint32_t (&rt)[8], float (&sum)[GPW]) {
     float acc[GPW][2];
 #pragma unroll
     for (int u = 0; u < GPW; ++u) acc[u][0] = acc[u][1] = 0.f;
@@ -215,73 +270,111 @@ __device__ __forceinline__ void lookup_word(const uint4 &w, const uint32_t (&rt)
     for (int wi = 0; wi < 4; ++wi) {
         const uint32_t word = words[wi];
         constexpr int kPerSub = 16 / GPW;
-        const int u0 = (4 * wi) / kPerSub;  // all four bytes of a word share a sub-group
-        acc[u0][0] += lds_f32_imm<0>(byte_into_base<0>(word, rt[2 * wi]));
-        acc[u0][1] += lds_f32_imm<128>(byte_into_base<1>(word, rt[2 * wi]));
-        acc[u0][0] += lds_f32_imm<0>(byte_into_base<2>(word, rt[2 * wi + 1]));
-        acc[u0][1] += lds_f32_imm<128>(byte_into_base<3>(word, rt[2 * wi + 1]));
+        const int u0 = (4 * wi) / kPerSub;  // the four bytes of a word share a sub-group
+        acc[u0][0] += lds_f32(byte_into_base<0>(word, rt[2 * wi]));
+        acc[u0][1] += lds_f32_hi(byte_into_base<1>(word, rt[2 * wi]));
+        acc[u0][0] += lds_f32(byte_into_base<2>(word, rt[2 * wi + 1]));
+        acc[u0][1] += lds_f32_hi(byte_into_base<3>(word, rt[2 * wi + 1]));
     }
 #pragma unroll
     for (int u = 0; u < GPW; ++u) sum[u] = acc[u][0] + acc[u][1];
 }
 
-template <int Q, int GPW, int OU>
-__device__ __forceinline__ void compute_tile(const Tile<Q, GPW, OU> &t, const GemvArgs &a,
-                                             const uint32_t (&rt)[8], const float (&xsu)[GPW],
-                                             int s, int oct0, int oct_end, int lane, int mrow) {
-    float v[OU];
+// One duo: both octs' totals, the 4-lane reduction, and the add into the row's fp32
+// accumulator (a reduction without return value: the slices of a row come from different
+// CTAs).  `prow` points at acc[row of (first oct, this lane's r)].
+template <int Q, int GPW>
+__device__ __forceinline__ void compute_tile(const Tile<Q, GPW> &t, const uint32_t (&rt)[8],
+                                             const float (&xsu)[GPW], float *prow, int lane) {
+    float v[2];
 #pragma unroll
-    for (int ou = 0; ou < OU; ++ou) {
+    for (int ou = 0; ou < 2; ++ou) {
         float tot = 0.f;
 #pragma unroll
-        for (int u = 0; u < GPW; ++u) tot += meta_value<GPW>(t.mt[ou][Q], u) * xsu[u];
+        for (int u = 0; u < GPW; ++u) tot += meta_value<GPW>(t.mt[Q], ou * GPW + u) * xsu[u];
 #pragma unroll
         for (int p = 0; p < Q; ++p) {
             float sum[GPW];
             lookup_word<GPW>(t.w[ou][p], rt, sum);
 #pragma unroll
-            for (int u = 0; u < GPW; ++u) tot += meta_value<GPW>(t.mt[ou][p], u) * sum[u];
+            for (int u = 0; u < GPW; ++u) tot += meta_value<GPW>(t.mt[p], ou * GPW + u) * sum[u];
         }
         v[ou] = tot;
     }
-    // reduce the four lanes (j = lane & 3) of each row; with OU > 1 the reduction also
-    // transposes, so that lane j ends up with oct oct0 + j
+    // lanes j = 0..3 of a row: after the exchange lane j < 2 holds oct j of the duo
     const int j = lane & 3;
-    float res;
-    int my_oct;
-    if (OU == 4) {
-        const bool odd = j & 1;
-        float k0 = odd ? v[1] : v[0], k1 = odd ? v[3] : v[2];
-        float s0 = odd ? v[0] : v[1], s1 = odd ? v[2] : v[3];
-        k0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-        k1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-        const bool hi = j & 2;
-        float keep = hi ? k1 : k0, send = hi ? k0 : k1;
-        keep += __shfl_xor_sync(0xffffffffu, send, 2);
-        res = keep;
-        my_oct = oct0 + j;
-    } else if (OU == 2) {
-        const bool odd = j & 1;
-        float keep = odd ? v[OU - 1] : v[0], send = odd ? v[0] : v[OU - 1];
-        keep += __shfl_xor_sync(0xffffffffu, send, 1);
-        keep += __shfl_xor_sync(0xffffffffu, keep, 2);
-        res = keep;
-        my_oct = (j < 2) ? oct0 + j : oct_end;  // lanes j >= 2 hold duplicates
+    const bool odd = j & 1;
+    float keep = odd ? v[1] : v[0];
+    const float send = odd ? v[0] : v[1];
+    keep += __shfl_xor_sync(0xffffffffu, send, 1);
+    keep += __shfl_xor_sync(0xffffffffu, keep, 2);
+    if (j < 2) atomicAdd(prow + j * kOctRows, keep);
+}
+
+// ---- control warp: walks the CTA's unit range and emits segment descriptors ---------------
+struct Walker {
+    const GemvArgs *a;
+    long long u, u_end;
+    int jidx;
+    Job jb;
+    int mrow;
+};
+
+__device__ __forceinline__ void walker_init(Walker &w, const GemvArgs &a, int mrow) {
+    w.a = &a;
+    w.u = a.total_units * blockIdx.x / gridDim.x;
+    w.u_end = a.total_units * (blockIdx.x + 1) / gridDim.x;
+    w.mrow = mrow;
+    w.jidx = 0;
+    if (a.njobs == 0) {
+        w.jb = a.single;
     } else {
-        float keep = v[0];
-        keep += __shfl_xor_sync(0xffffffffu, keep, 1);
-        keep += __shfl_xor_sync(0xffffffffu, keep, 2);
-        res = keep;
-        my_oct = (j == 0) ? oct0 : oct_end;
-    }
-    if (my_oct < oct_end) {
-        const int row = my_oct * kOctRows + (lane >> 2);
-        a.partial[((int64_t)mrow * a.slices + s) * a.np + row] = res;
+        // binary search for the job that holds unit u
+        int lo = 0, hi = a.njobs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.jobs[mid].unit_begin <= w.u) lo = mid; else hi = mid - 1;
+        }
+        w.jidx = lo;
+        w.jb = a.jobs[lo];
     }
 }
 
-template <int Q, int GPW, int OU>
-__global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const GemvArgs a) {
+// Fills `sg` with the next segment and returns the activation slice to copy (or nullptr).
+template <int Q, int GPW>
+__device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &valid) {
+    sg.live = 0;
+    valid = 0;
+    if (w.u >= w.u_end) return nullptr;
+    while (w.u >= w.jb.unit_begin + (long long)w.jb.slices * w.jb.duos && w.jidx + 1 < w.a->njobs) {
+        ++w.jidx;
+        w.jb = w.a->jobs[w.jidx];
+    }
+    const Job &jb = w.jb;
+    const long long local = w.u - jb.unit_begin;
+    const int s = (int)(local / jb.duos);
+    const int da = (int)(local % jb.duos);
+    const long long left = w.u_end - w.u;
+    const int db = (int)((long long)(jb.duos - da) < left ? jb.duos : da + left);
+    const long long cell = (long long)s * jb.duos + da;           // in duos
+    sg.planes = jb.planes + cell * (2 * Q * kCellBytes);
+    sg.meta = jb.meta + cell * ((Q + 1) * 32 * 2 * GPW);
+    sg.bias = jb.bias;
+    sg.acc = jb.acc + (long long)w.mrow * jb.np;
+    sg.counters = jb.counters + (long long)w.mrow * jb.blocks;
+    sg.y = jb.y;
+    sg.y_base = (long long)w.mrow * jb.n;
+    sg.n = jb.n; sg.np = jb.np; sg.slices = jb.slices;
+    sg.duo_a = da; sg.duo_b = db;
+    sg.x_dtype = jb.x_dtype; sg.y_dtype = jb.y_dtype;
+    sg.live = 1;
+    valid = min(kSliceK, jb.k - s * kSliceK);
+    w.u += db - da;
+    return (const uint16_t *)jb.x + (long long)w.mrow * jb.k + (long long)s * kSliceK;
+}
+
+template <int Q, int GPW>
+__global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_constant__ GemvArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int mrow = blockIdx.y;
@@ -295,92 +388,177 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const GemvArgs a
         return;
     }
     unsigned char *aux = smem_raw + (aux_u32 - sbase);
-    uint16_t *xs = (uint16_t *)(aux + kAuxX);
     float *xsum = (float *)(aux + kAuxXsum);
-    const uint32_t mbar = aux_u32 + kAuxMbar;
-    int *list_n = (int *)(aux + kAuxListN);
     int *fail = (int *)(aux + kAuxFlag);
-    int *list = (int *)(aux + kAuxList);
+    Seg *ring = (Seg *)(aux + kAuxSeg);
+    const uint32_t mb_desc = aux_u32 + kAuxMbarDesc, mb_x = aux_u32 + kAuxMbarX;
 
     pdl_launch_dependents();
-
     if (tid == 0) {
-        mbar_init(mbar, 1);
+        mbar_init(mb_desc, 1);
+        mbar_init(mb_desc + 8, 1);
+        mbar_init(mb_x, 1);
+        mbar_init(mb_x + 8, 1);
+        mbar_init_fence();
         *fail = 0;
     }
-
-    // per-lane lookup bases: bank 8*j + (t ^ r) of the table row
-    const int r = lane >> 2, j = lane & 3;
-    uint32_t rt[8];
-#pragma unroll
-    for (int t = 0; t < 8; ++t) rt[t] = tbl + 4u * (8u * j + (uint32_t)(t ^ r));
-
-    // contiguous range of (slice, oct) units of this CTA
-    const int64_t units = (int64_t)a.slices * a.octs;
-    int64_t u = units * blockIdx.x / gridDim.x;
-    const int64_t u_end = units * (blockIdx.x + 1) / gridDim.x;
-
-    constexpr int gshift = GPW == 1 ? 3 : (GPW == 2 ? 2 : 1);
-    uint32_t phase = 0;
-    bool first = true;
-
     __syncthreads();
 
-    while (u < u_end) {
-        const int s = (int)(u / a.octs);
-        const int oa = (int)(u % a.octs);
-        const int ob = (int)min((int64_t)a.octs, oa + (u_end - u));
-
-        // 1. start streaming weights (they do not depend on the activations)
-        Tile<Q, GPW, OU> ta, tb;
-        int o = oa + warp * OU;
-        constexpr int ostride = kWarps * OU;
-        if (o < ob) load_tile<Q, GPW, OU>(ta, a, s, o, ob, lane);
-
-        // 2. activations of this slice: TMA bulk copy + zero padding
-        if (first) {
-            pdl_wait();
-            first = false;
+    if (warp >= kConsumerWarps) {
+        // =========================== finalizer warps ======================================
+        const int fw = warp - kConsumerWarps, ftid = tid - kConsumers;
+        Walker wk;
+        bool waited = false;
+        auto emit = [&](int slot) {   // control warp only
+            Seg sg;
+            int valid;
+            const uint16_t *src = walker_next<Q, GPW>(wk, sg, valid);
+            if (lane == 0) ring[slot] = sg;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(mb_desc + 8 * slot);
+            if (sg.live) {
+                if (!waited) {
+                    pdl_wait();
+                    waited = true;
+                }
+                uint16_t *xs = (uint16_t *)(aux + kAuxX) + slot * kSliceK;
+                for (int i = valid + lane; i < kSliceK; i += 32) xs[i] = 0;
+                __syncwarp();
+                if (lane == 0) {
+                    fence_proxy_async();
+                    mbar_expect_tx(mb_x + 8 * slot, (uint32_t)valid * 2u);
+                    tma_bulk_g2s(aux_u32 + kAuxX + slot * kSliceK * 2, src, (uint32_t)valid * 2u,
+                                 mb_x + 8 * slot);
+                }
+            }
+        };
+        if (fw == 0) {
+            walker_init(wk, a, mrow);
+            emit(0);
+            emit(1);
+        } else {
+            pdl_wait();   // before this warp's first global write
         }
-        const int valid = min(kSliceK, a.k - s * kSliceK);
-        if (tid == 0) {
-            fence_proxy_async();
-            mbar_expect_tx(mbar, (uint32_t)valid * 2u);
-            const uint16_t *src = (const uint16_t *)a.x + (int64_t)mrow * a.k + (int64_t)s * kSliceK;
-            tma_bulk_g2s(aux_u32 + kAuxX, src, (uint32_t)valid * 2u, mbar);
+        for (int i = 0;; ++i) {
+            const int slot = i & 1;
+            if (!mbar_wait_bounded(mb_desc + 8 * slot, (i >> 1) & 1)) *fail = 1;
+            const Seg sg = ring[slot];
+            if (!sg.live) break;
+            named_bar_sync_dyn(kBarSegDone + slot, kThreads);      // consumers are done with it
+            named_bar_sync<kBarFinalizers, kFinalizers>();         // every finalizer holds its copy
+            if (fw == 0) emit(slot);                               // segment i + 2
+            // publish: count finished duos per 32-row block; whoever completes a block sums it
+            const int bfirst = sg.duo_a >> 1, blast = (sg.duo_b - 1) >> 1;
+            const unsigned total = (unsigned)sg.slices * 2u;
+            for (int b0 = bfirst; b0 <= blast; b0 += kFinalizers) {
+                const int blk = b0 + ftid;
+                bool mine = false;
+                if (blk <= blast) {
+                    const int lo = max(sg.duo_a, 2 * blk), hi = min(sg.duo_b, 2 * blk + 2);
+                    const unsigned cnt = (unsigned)(hi - lo);
+                    __threadfence();
+                    const unsigned old = atomicAdd(&sg.counters[blk], cnt);
+                    mine = (old + cnt == total);
+                }
+                unsigned mask = __ballot_sync(0xffffffffu, mine);
+                if (mask) __threadfence();
+                // lane = row of a finished block; several blocks per round trip
+                while (mask) {
+                    float v[8];
+                    int rows[8];
+                    unsigned mm = mask;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        rows[b] = -1;
+                        if (mm) {
+                            const int src_lane = __ffs(mm) - 1;
+                            mm &= mm - 1;
+                            rows[b] = __shfl_sync(0xffffffffu, blk, src_lane) * kBlockRows + lane;
+                            v[b] = ldcg_f32(sg.acc + rows[b]);
+                        }
+                    }
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        if (rows[b] >= 0) {
+                            sg.acc[rows[b]] = 0.f;
+                            if (rows[b] < sg.n) {
+                                float o = v[b];
+                                if (sg.bias) o += __half2float(__ushort_as_half(sg.bias[rows[b]]));
+                                store_y(sg.y, sg.y_base + rows[b], o, sg.y_dtype);
+                            }
+                            if (lane == 0) sg.counters[rows[b] / kBlockRows] = 0;
+                        }
+                    }
+                    mask = mm;
+                }
+            }
         }
-        if (tid >= valid && tid < kSliceK) xs[tid] = 0;
-        const bool ok = mbar_wait_bounded(mbar, phase);
-        phase ^= 1u;
-        if (!ok) *fail = 1;
-        __syncthreads();
-        if (*fail) {
-            if (tid == 0) atomicExch(a.status, 1);
-            return;  // the copy was given 2^22 polls; nothing else of this CTA is in flight
-        }
+        if (*fail && ftid == 0) atomicExch(a.status, 1);
+        return;
+    }
 
-        // 3. group sums (warp 0) and the 64 tables of 256 subset sums (all warps)
+    // =============================== consumer warps =======================================
+    const int r = lane >> 2, j = lane & 3;
+    uint32_t rt[8];   // per-lane lookup bases: bank 8*j + (t ^ r) of the table row
+#pragma unroll
+    for (int t = 0; t < 8; ++t) rt[t] = tbl + 4u * (8u * j + (uint32_t)(t ^ r));
+    constexpr int gshift = GPW == 1 ? 3 : (GPW == 2 ? 2 : 1);
+    constexpr long long kDuoPlaneBytes = 2 * Q * kCellBytes;
+    constexpr long long kDuoMetaElems = (Q + 1) * 32 * 2 * GPW;
+
+    // Register tiles in flight: three where a tile is small enough, else two.
+    constexpr int kRing = (8 * Q + (Q + 1) * GPW < 22) ? 3 : 2;
+    Tile<Q, GPW> t0, t1, t2;
+    // running state of the current segment
+    const uint8_t *pl;
+    const uint16_t *mp;
+    float *prow;
+    int d, dend, x_dtype;
+
+    auto open_segment = [&](const Seg &sg) {
+        d = sg.duo_a + warp;
+        dend = sg.duo_b;
+        x_dtype = sg.x_dtype;
+        pl = sg.planes + (long long)warp * kDuoPlaneBytes + lane * 16;
+        mp = sg.meta + (long long)warp * kDuoMetaElems + lane * (2 * GPW);
+        prow = sg.acc + (long long)d * 16 + r;
+        if (d < dend) load_tile<Q, GPW>(t0, pl, mp);
+        if (kRing == 3 && d + kConsumerWarps < dend)
+            load_tile<Q, GPW>(t1, pl + kConsumerWarps * kDuoPlaneBytes, mp + kConsumerWarps * kDuoMetaElems);
+    };
+
+    if (!mbar_wait_bounded(mb_desc, 0)) *fail = 1;
+    {
+        const Seg sg = ring[0];
+        if (!sg.live) return;
+        open_segment(sg);
+    }
+    for (int i = 0;; ++i) {
+        const int slot = i & 1;
+        named_bar_sync<kBarConsumers, kConsumers>();     // everyone is done with the old table
+        if (!mbar_wait_bounded(mb_x + 8 * slot, (i >> 1) & 1)) *fail = 1;
+        if (i == 0) pdl_wait();   // satisfied by now; orders this thread's writes after the previous grid
+        const uint16_t *xs = (const uint16_t *)(aux + kAuxX) + slot * kSliceK;
+        // group sums (warp 0) and the 64 tables of 256 subset sums (all consumer warps)
         if (warp == 0) {
             float part = 0.f;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) part += x_to_float(xs[lane * 16 + i], a.x_dtype);
-            // a group is g / 16 consecutive lanes: 8, 4 or 2
+            for (int q2 = 0; q2 < 16; ++q2) part += x_to_float(xs[lane * 16 + q2], x_dtype);
+            constexpr int lanes_per_group = 8 >> (3 - gshift);   // g / 16 lanes: 8, 4 or 2
 #pragma unroll
-            for (int d = 1; d < (8 >> (3 - gshift)); d <<= 1)
-                part += __shfl_xor_sync(0xffffffffu, part, d);
-            constexpr int lanes_per_group = 8 >> (3 - gshift);
+            for (int dd = 1; dd < lanes_per_group; dd <<= 1) part += __shfl_xor_sync(0xffffffffu, part, dd);
             if ((lane & (lanes_per_group - 1)) == 0) xsum[lane / lanes_per_group] = part;
         }
         {
-            const int h = warp & 1, ehi = warp >> 1;  // bank-row, top three index bits
+            const int h = warp & 1, ehi = warp >> 1;   // bank-row, top three index bits
             const int c = 16 * (lane >> 3) + 2 * (lane & 7) + h;
             const uint4 raw = *(const uint4 *)(xs + 8 * c);
             const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
             float xv[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                xv[2 * i] = x_to_float((uint16_t)(rw[i] & 0xffffu), a.x_dtype);
-                xv[2 * i + 1] = x_to_float((uint16_t)(rw[i] >> 16), a.x_dtype);
+            for (int q2 = 0; q2 < 4; ++q2) {
+                xv[2 * q2] = x_to_float((uint16_t)(rw[q2] & 0xffffu), x_dtype);
+                xv[2 * q2 + 1] = x_to_float((uint16_t)(rw[q2] >> 16), x_dtype);
             }
             float base = 0.f;
             if (ehi & 1) base += xv[5];
@@ -396,62 +574,55 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const GemvArgs a
 #pragma unroll
             for (int e = 0; e < 32; ++e) sts_f32(dst + (uint32_t)e * 256u, tv[e]);
         }
-        __syncthreads();
+        named_bar_sync<kBarConsumers, kConsumers>();
         asm volatile("" ::: "memory");
 
         float xsu[GPW];
 #pragma unroll
         for (int uu = 0; uu < GPW; ++uu) xsu[uu] = xsum[GPW * j + (uu ^ (r >> gshift))];
 
-        // 4. stream: ping-pong between two register tiles
-        while (o < ob) {
-            int on = o + ostride;
-            if (on < ob) load_tile<Q, GPW, OU>(tb, a, s, on, ob, lane);
-            compute_tile<Q, GPW, OU>(ta, a, rt, xsu, s, o, ob, lane, mrow);
-            o = on;
-            if (o >= ob) break;
-            on = o + ostride;
-            if (on < ob) load_tile<Q, GPW, OU>(ta, a, s, on, ob, lane);
-            compute_tile<Q, GPW, OU>(tb, a, rt, xsu, s, o, ob, lane, mrow);
-            o = on;
+        // stream: ring of three register tiles, two loads in flight behind the one in use
+        constexpr long long kStepP = kConsumerWarps * kDuoPlaneBytes;
+        constexpr long long kStepM = kConsumerWarps * kDuoMetaElems;
+        constexpr int kStepRow = kConsumerWarps * 16;
+        if (kRing == 3) {
+            while (d < dend) {
+                if (d + 2 * kConsumerWarps < dend) load_tile<Q, GPW>(t2, pl + 2 * kStepP, mp + 2 * kStepM);
+                compute_tile<Q, GPW>(t0, rt, xsu, prow, lane);
+                d += kConsumerWarps;
+                if (d >= dend) break;
+                if (d + 2 * kConsumerWarps < dend) load_tile<Q, GPW>(t0, pl + 3 * kStepP, mp + 3 * kStepM);
+                compute_tile<Q, GPW>(t1, rt, xsu, prow + kStepRow, lane);
+                d += kConsumerWarps;
+                if (d >= dend) break;
+                if (d + 2 * kConsumerWarps < dend) load_tile<Q, GPW>(t1, pl + 4 * kStepP, mp + 4 * kStepM);
+                compute_tile<Q, GPW>(t2, rt, xsu, prow + 2 * kStepRow, lane);
+                d += kConsumerWarps;
+                pl += 3 * kStepP;
+                mp += 3 * kStepM;
+                prow += 3 * kStepRow;
+            }
+        } else {
+            while (d < dend) {
+                if (d + kConsumerWarps < dend) load_tile<Q, GPW>(t1, pl + kStepP, mp + kStepM);
+                compute_tile<Q, GPW>(t0, rt, xsu, prow, lane);
+                d += kConsumerWarps;
+                if (d >= dend) break;
+                if (d + kConsumerWarps < dend) load_tile<Q, GPW>(t0, pl + 2 * kStepP, mp + 2 * kStepM);
+                compute_tile<Q, GPW>(t1, rt, xsu, prow + kStepRow, lane);
+                d += kConsumerWarps;
+                pl += 2 * kStepP;
+                mp += 2 * kStepM;
+                prow += 2 * kStepRow;
+            }
         }
 
-        // 5. publish: count finished octs per 32-row block; whoever completes a block sums it
-        __threadfence();
-        __syncthreads();
-        const int bfirst = oa >> 2, blast = (ob - 1) >> 2;
-        const unsigned total = (unsigned)a.slices * 4u;
-        for (int b0 = bfirst; b0 <= blast; b0 += kListCap) {
-            if (tid == 0) *list_n = 0;
-            __syncthreads();
-            const int blk = b0 + tid;
-            if (tid < kListCap && blk <= blast) {
-                const int lo = max(oa, 4 * blk), hi = min(ob, 4 * blk + 4);
-                const unsigned cnt = (unsigned)(hi - lo);
-                __threadfence();
-                const unsigned old = atomicAdd(&a.counters[(int64_t)mrow * a.blocks + blk], cnt);
-                if (old + cnt == total) list[atomicAdd(list_n, 1)] = blk;
-            }
-            __syncthreads();
-            const int nlist = *list_n;
-            if (nlist > 0) {
-                __threadfence();
-                for (int li = warp; li < nlist; li += kWarps) {
-                    const int blk2 = list[li];
-                    const int row = blk2 * kBlockRows + lane;
-                    const float *pp = a.partial + (int64_t)mrow * a.slices * a.np + row;
-                    float acc = 0.f;
-                    for (int ss = 0; ss < a.slices; ++ss) acc += ldcg_f32(pp + (int64_t)ss * a.np);
-                    if (row < a.n) {
-                        if (a.bias) acc += __half2float(__ushort_as_half(a.bias[row]));
-                        store_y(a.y, (int64_t)mrow * a.n + row, acc, a.y_dtype);
-                    }
-                    if (lane == 0) a.counters[(int64_t)mrow * a.blocks + blk2] = 0;
-                }
-            }
-            __syncthreads();
-        }
-        u += ob - oa;
+        // first loads of the next segment, then hand this one to the finalizers
+        if (!mbar_wait_bounded(mb_desc + 8 * (slot ^ 1), ((i + 1) >> 1) & 1)) *fail = 1;
+        const Seg nx = ring[slot ^ 1];
+        if (nx.live) open_segment(nx);
+        named_bar_arrive_dyn(kBarSegDone + slot, kThreads);
+        if (!nx.live) break;
     }
 }
 
@@ -492,6 +663,7 @@ __global__ void __launch_bounds__(kGenThreads) lut4_gemv_kernel(const GenArgs a)
     pdl_launch_dependents();
     if (tid == 0) {
         mbar_init(mbar, 1);
+        mbar_init_fence();
         fail = 0;
     }
     for (int i = tid; i < rows; i += kGenThreads) yacc[i] = 0.f;
@@ -611,7 +783,7 @@ __global__ void __launch_bounds__(kGenThreads) lut4_gemv_kernel(const GenArgs a)
 size_t workspace_bytes_for(int m, const StreamDims &d) {
     const int mm = m < kLutMaxM ? m : kLutMaxM;
     size_t counters = ((size_t)mm * d.blocks * sizeof(unsigned) + 255) / 256 * 256;
-    size_t partial = (size_t)mm * d.slices * d.np * sizeof(float);
+    size_t partial = (size_t)mm * d.np * sizeof(float);
     return kWsHeader + counters + partial;
 }
 
@@ -671,12 +843,12 @@ static int launch_pdl(KernelT kernel, dim3 grid, dim3 block, size_t smem, cudaSt
 // wherever the window starts: 64 KB of slack, the table, the aux area.
 constexpr uint32_t kLut8DynSmem = 65536 - 1024 + kTableBytes + kAuxBytes;
 
-template <int Q, int GPW, int OU>
+template <int Q, int GPW>
 static int launch_lut8_inst(const GemvArgs &args, dim3 grid, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     HLQ_CUDA(cudaGetDevice(&dev));
-    auto kernel = lut8_gemv_kernel<Q, GPW, OU>;
+    auto kernel = lut8_gemv_kernel<Q, GPW>;
     if (!configured[dev & 63]) {
         HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)kLut8DynSmem));
@@ -685,23 +857,34 @@ static int launch_lut8_inst(const GemvArgs &args, dim3 grid, cudaStream_t stream
     return launch_pdl(kernel, grid, dim3(kThreads), kLut8DynSmem, stream, args);
 }
 
-template <int Q, int GPW>
-static int launch_lut8_ou(int ou, const GemvArgs &args, dim3 grid, cudaStream_t stream) {
-    if (Q <= 2 && ou >= 4) return launch_lut8_inst<Q, GPW, (Q <= 2 ? 4 : 2)>(args, grid, stream);
-    if (ou >= 2) return launch_lut8_inst<Q, GPW, 2>(args, grid, stream);
-    return launch_lut8_inst<Q, GPW, 1>(args, grid, stream);
-}
-
-template <int Q>
-static int launch_lut8_gpw(int gpw, int ou, const GemvArgs &args, dim3 grid, cudaStream_t stream) {
-    if (gpw == 1) return launch_lut8_ou<Q, 1>(ou, args, grid, stream);
-    if (gpw == 2) return launch_lut8_ou<Q, 2>(ou, args, grid, stream);
-    return launch_lut8_ou<Q, 4>(ou, args, grid, stream);
+static int launch_lut8_any(int q, int gpw, const GemvArgs &a, dim3 grid, cudaStream_t stream) {
+#define HLQ_CASE(QV, GV) \
+    if (q == QV && gpw == GV) return launch_lut8_inst<QV, GV>(a, grid, stream);
+    HLQ_CASE(1, 1) HLQ_CASE(1, 2) HLQ_CASE(1, 4)
+    HLQ_CASE(2, 1) HLQ_CASE(2, 2) HLQ_CASE(2, 4)
+    HLQ_CASE(3, 1) HLQ_CASE(3, 2) HLQ_CASE(3, 4)
+    HLQ_CASE(4, 1) HLQ_CASE(4, 2) HLQ_CASE(4, 4)
+#undef HLQ_CASE
+    return HLQ_ERR_SHAPE;
 }
 
 static int env_int(const char *name, int dflt) {
     const char *v = getenv(name);
     return v && *v ? atoi(v) : dflt;
+}
+
+static void fill_job(Job &j, const hlq_weight *w, const StreamDims &d, const void *x, int x_dtype,
+                     void *y, int y_dtype, float *partial, unsigned *counters, long long unit_begin) {
+    j.planes = w->d_planes;
+    j.meta = w->d_meta;
+    j.bias = w->d_bias;
+    j.acc = partial;
+    j.counters = counters;
+    j.x = x;
+    j.y = y;
+    j.n = w->n; j.k = w->k; j.np = d.np; j.slices = d.slices; j.duos = d.duos; j.blocks = d.blocks;
+    j.x_dtype = x_dtype; j.y_dtype = y_dtype;
+    j.unit_begin = unit_begin;
 }
 
 int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
@@ -716,42 +899,192 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
     if (rc) return rc;
     if ((uint32_t)di->max_dyn_smem < kLut8DynSmem) return HLQ_ERR_NO_DEVICE;
 
-    static const int force_ou = env_int("HLQ_GEMV_OU", 0);
     static const int force_ctas = env_int("HLQ_GEMV_CTAS", 0);
     const size_t xsz = 2, ysz = y_dtype == HLQ_F32 ? 4 : 2;
     for (int m0 = 0; m0 < m; m0 += kLutMaxM) {
         const int mc = (m - m0) < kLutMaxM ? (m - m0) : kLutMaxM;
         const Workspace ws = carve_workspace(workspace, mc, d);
-        GemvArgs a;
-        a.planes = w->d_planes;
-        a.meta = w->d_meta;
-        a.x = (const char *)x + (size_t)m0 * w->k * xsz;
-        a.y = (char *)y + (size_t)m0 * w->n * ysz;
-        a.bias = w->d_bias;
-        a.partial = ws.partial;
-        a.counters = ws.counters;
+        GemvArgs a = {};
+        a.jobs = nullptr;
+        a.njobs = 0;
+        a.total_units = (long long)d.slices * d.duos;
         a.status = ws.status;
-        a.n = w->n; a.k = w->k; a.np = d.np; a.slices = d.slices; a.octs = d.octs;
-        a.blocks = d.blocks;
-        a.x_dtype = x_dtype; a.y_dtype = y_dtype;
         a.dyn_smem = kLut8DynSmem;
-        const int64_t units = (int64_t)d.slices * d.octs;
+        fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
+                 (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         int ctas = force_ctas > 0 ? force_ctas : di->sms;
-        if (units < ctas) ctas = (int)units;
-        const int64_t per_cta = units / ctas;
-        int ou = force_ou > 0 ? force_ou : (per_cta >= 10 * kWarps ? 4 : (per_cta >= 3 * kWarps ? 2 : 1));
-        dim3 grid(ctas, mc);
-        switch (w->q) {
-            case 1: rc = launch_lut8_gpw<1>(d.gpw, ou, a, grid, stream); break;
-            case 2: rc = launch_lut8_gpw<2>(d.gpw, ou, a, grid, stream); break;
-            case 3: rc = launch_lut8_gpw<3>(d.gpw, ou, a, grid, stream); break;
-            case 4: rc = launch_lut8_gpw<4>(d.gpw, ou, a, grid, stream); break;
-            default: rc = HLQ_ERR_SHAPE;
-        }
+        if (a.total_units < ctas) ctas = (int)a.total_units;
+        rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream);
         if (rc) return rc;
     }
     return HLQ_OK;
 }
+
+}  // namespace hlq
+
+// ---- groups: many independent linears in one persistent launch -----------------------------
+struct hlq_group {
+    int device = 0;
+    int count = 0, max_m = 1;
+    int q = 0, gpw = 0;
+    long long total_units = 0;
+    std::vector<const hlq_weight *> weights;
+    std::vector<hlq::Job> jobs_host;
+    hlq::Job *d_jobs = nullptr;
+    unsigned char *d_scratch = nullptr;   // status word, counters and partial sums of all jobs
+    size_t scratch_bytes = 0;
+    bool bound = false;
+};
+
+using namespace hlq;
+
+extern "C" {
+
+int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weights, int max_m) {
+    if (!out) return HLQ_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    if (count <= 0 || !weights || max_m < 1 || max_m > kLutMaxM) return HLQ_ERR_INVALID_ARGUMENT;
+    for (int i = 0; i < count; ++i) {
+        if (!weights[i]) return HLQ_ERR_INVALID_ARGUMENT;
+        if (weights[i]->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
+        if (weights[i]->q != weights[0]->q || weights[i]->g != weights[0]->g ||
+            weights[i]->device != weights[0]->device)
+            return HLQ_ERR_UNSUPPORTED;
+    }
+    hlq_group *g = new (std::nothrow) hlq_group();
+    if (!g) return HLQ_ERR_INVALID_ARGUMENT;
+    g->device = weights[0]->device;
+    g->count = count;
+    g->max_m = max_m;
+    g->q = weights[0]->q;
+    g->weights.assign(weights, weights + count);
+    g->jobs_host.resize(count);
+    // scratch: [status 256 B][per job: counters, partial]
+    size_t off = kWsHeader;
+    std::vector<size_t> coff(count), poff(count);
+    long long units = 0;
+    for (int i = 0; i < count; ++i) {
+        const hlq_weight *w = weights[i];
+        const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
+        g->gpw = d.gpw;
+        coff[i] = off;
+        off += ((size_t)max_m * d.blocks * sizeof(unsigned) + 255) / 256 * 256;
+        poff[i] = off;
+        off += ((size_t)max_m * d.np * sizeof(float) + 255) / 256 * 256;
+        units += (long long)d.slices * d.duos;
+    }
+    g->scratch_bytes = off;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    int rc = HLQ_OK;
+    if (cudaSetDevice(g->device) != cudaSuccess) rc = HLQ_ERR_NO_DEVICE;
+    if (!rc && cudaMalloc((void **)&g->d_scratch, off) != cudaSuccess) rc = note_cuda(cudaErrorMemoryAllocation);
+    if (!rc && cudaMalloc((void **)&g->d_jobs, sizeof(Job) * count) != cudaSuccess)
+        rc = note_cuda(cudaErrorMemoryAllocation);
+    if (!rc) rc = note_cuda(cudaMemset(g->d_scratch, 0, off));
+    if (!rc) {
+        long long ub = 0;
+        for (int i = 0; i < count; ++i) {
+            const hlq_weight *w = weights[i];
+            const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
+            fill_job(g->jobs_host[i], w, d, nullptr, HLQ_F16, nullptr, HLQ_F16,
+                     (float *)(g->d_scratch + poff[i]), (unsigned *)(g->d_scratch + coff[i]), ub);
+            ub += (long long)d.slices * d.duos;
+        }
+        g->total_units = ub;
+    }
+    if (prev >= 0) cudaSetDevice(prev);
+    if (rc) {
+        if (g->d_scratch) cudaFree(g->d_scratch);
+        if (g->d_jobs) cudaFree(g->d_jobs);
+        delete g;
+        return rc;
+    }
+    *out = g;
+    return HLQ_OK;
+}
+
+int hlq_group_bind(hlq_group *g, const void *const *d_x, void *const *d_y, int x_dtype, int y_dtype,
+                   void *stream) {
+    if (!g || !d_x || !d_y) return HLQ_ERR_INVALID_ARGUMENT;
+    if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
+    if (y_dtype != HLQ_F16 && y_dtype != HLQ_BF16 && y_dtype != HLQ_F32) return HLQ_ERR_UNSUPPORTED;
+    for (int i = 0; i < g->count; ++i) {
+        if (!d_x[i] || !d_y[i]) return HLQ_ERR_INVALID_ARGUMENT;
+        if (((uintptr_t)d_x[i] & 15) || ((uintptr_t)d_y[i] & 3)) return HLQ_ERR_ALIGNMENT;
+        g->jobs_host[i].x = d_x[i];
+        g->jobs_host[i].y = d_y[i];
+        g->jobs_host[i].x_dtype = x_dtype;
+        g->jobs_host[i].y_dtype = y_dtype;
+    }
+    // the table is small; a synchronous copy keeps the host vector free to change afterwards
+    HLQ_CUDA(cudaMemcpyAsync(g->d_jobs, g->jobs_host.data(), sizeof(Job) * g->count, cudaMemcpyHostToDevice,
+                             (cudaStream_t)stream));
+    HLQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    g->bound = true;
+    return HLQ_OK;
+}
+
+int hlq_group_forward(hlq_group *g, int m, void *stream) {
+    if (!g || m < 0) return HLQ_ERR_INVALID_ARGUMENT;
+    if (m == 0) return HLQ_OK;
+    if (!g->bound) return HLQ_ERR_INVALID_ARGUMENT;
+    if (m > g->max_m) return HLQ_ERR_WORKSPACE;
+    int cur = -1;
+    HLQ_CUDA(cudaGetDevice(&cur));
+    if (cur != g->device) return HLQ_ERR_INVALID_ARGUMENT;
+    DeviceInfo *di;
+    int rc = device_info(g->device, &di);
+    if (rc) return rc;
+    if ((uint32_t)di->max_dyn_smem < kLut8DynSmem) return HLQ_ERR_NO_DEVICE;
+    static const int force_ctas = env_int("HLQ_GEMV_CTAS", 0);
+    GemvArgs a = {};
+    a.jobs = g->d_jobs;
+    a.njobs = g->count;
+    a.total_units = g->total_units;
+    a.status = (int *)g->d_scratch;
+    a.dyn_smem = kLut8DynSmem;
+    int ctas = force_ctas > 0 ? force_ctas : di->sms;
+    if (a.total_units < ctas) ctas = (int)a.total_units;
+    return launch_lut8_any(g->q, g->gpw, a, dim3(ctas, m), (cudaStream_t)stream);
+}
+
+int hlq_group_status(const hlq_group *g, void *stream, int *kernel_status) {
+    if (!g || !kernel_status) return HLQ_ERR_INVALID_ARGUMENT;
+    HLQ_CUDA(cudaMemcpyAsync(kernel_status, g->d_scratch, sizeof(int), cudaMemcpyDeviceToHost,
+                             (cudaStream_t)stream));
+    HLQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return *kernel_status ? HLQ_ERR_KERNEL : HLQ_OK;
+}
+
+int hlq_group_info(const hlq_group *g, int *count, int64_t *scratch_bytes, int64_t *algorithmic_bytes) {
+    if (!g) return HLQ_ERR_INVALID_ARGUMENT;
+    if (count) *count = g->count;
+    if (scratch_bytes) *scratch_bytes = (int64_t)g->scratch_bytes;
+    if (algorithmic_bytes) {
+        int64_t t = 0;
+        for (const hlq_weight *w : g->weights)
+            t += (int64_t)w->q * w->n * (w->k / 8) + 2 * (int64_t)(w->q + 1) * w->n * (w->k / w->g);
+        *algorithmic_bytes = t;
+    }
+    return HLQ_OK;
+}
+
+int hlq_group_free(hlq_group *g) {
+    if (!g) return HLQ_OK;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(g->device);
+    if (g->d_scratch) cudaFree(g->d_scratch);
+    if (g->d_jobs) cudaFree(g->d_jobs);
+    if (prev >= 0) cudaSetDevice(prev);
+    delete g;
+    return HLQ_OK;
+}
+
+}  // extern "C"
+
+namespace hlq {
 
 // Status word used by the generic kernel when the caller gave no workspace.
 static int *generic_status_word(int device) {

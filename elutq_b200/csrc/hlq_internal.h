@@ -33,14 +33,14 @@ void count_launch(int n = 1);
         if (e__ != cudaSuccess) return hlq::note_cuda(e__); \
     } while (0)
 
-// Workspace layout: [0, 256) header (int status at 0), then counters, then partial sums.
+// Workspace layout: [0, 256) header (int status at 0), then counters, then accumulators.
 constexpr size_t kWsHeader = 256;
 constexpr int kLutMaxM = 16;  // rows of x one LUT-GEMV launch handles
 
 struct Workspace {
     int *status;
     unsigned *counters;  // [m][blocks]
-    float *partial;      // [m][slices][np]
+    float *partial;      // [m][np] fp32 accumulators
 };
 size_t workspace_bytes_for(int m, const StreamDims &d);
 Workspace carve_workspace(void *base, int m, const StreamDims &d);

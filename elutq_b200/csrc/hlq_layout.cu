@@ -74,12 +74,14 @@ __global__ void repack_meta_kernel(const uint16_t *__restrict__ w_scale,
         int64_t t = idx;
         const int u = (int)(t % d.gpw);
         t /= d.gpw;
+        const int ou = (int)(t & 1);
+        t >>= 1;
         const int lane = (int)(t & 31);
         t >>= 5;
         const int pp = (int)(t % (d.q + 1));
         t /= (d.q + 1);
-        const int oct = (int)(t % d.octs);
-        const int s = (int)(t / d.octs);
+        const int oct = (int)(t % d.duos) * 2 + ou;
+        const int s = (int)(t / d.duos);
         const int r = lane >> 2, j = lane & 3;
         const int64_t row = (int64_t)oct * kOctRows + r;
         const int64_t grp = ((int64_t)s * kSliceK + 128 * j) / d.g + stream_src_group(d, u, r);

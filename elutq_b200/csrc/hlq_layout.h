@@ -10,10 +10,11 @@
 // 8*j + ((i >> 1) ^ r): the 32 lanes of a warp always touch 32 different banks.
 //
 // Cells are stored slice-major:  planes[s][oct][plane][lane][16].
-// Scales and zeros follow the same ownership:  meta[s][oct][pp][lane][u] (fp16), pp < q the
-// plane's scale, pp == q the zero; u < gpw = 128 / g indexes the groups inside the lane's
-// 128 channels BY BYTE POSITION, i.e. entry u belongs to source group u ^ (r >> log2(g/16)).
-// Rows >= n, channels >= k and their groups are stored as zeros.
+// Scales and zeros follow the same ownership, two octs (a DUO, 16 rows) at a time so that a
+// lane fetches both octs of a duo with one load:  meta[s][duo][pp][lane][oct & 1][u] (fp16),
+// pp < q the plane's scale, pp == q the zero; u < gpw = 128 / g indexes the groups inside the
+// lane's 128 channels BY BYTE POSITION, i.e. entry u belongs to source group
+// u ^ (r >> log2(g/16)).  Rows >= n, channels >= k and their groups are stored as zeros.
 #pragma once
 #include <stdint.h>
 
@@ -36,6 +37,7 @@ struct StreamDims {
     int kp;     // k rounded up to 512
     int slices; // kp / 512
     int octs;   // np / 8
+    int duos;   // np / 16
     int blocks; // np / 32
     int gpw;    // groups per 128 channels: 128 / g
     int gshift; // log2(g / 16): 3, 2, 1 for g = 128, 64, 32
@@ -50,6 +52,7 @@ HLQ_HD StreamDims stream_dims(int n, int k, int g, int q) {
     d.kp = (k + kSliceK - 1) / kSliceK * kSliceK;
     d.slices = d.kp / kSliceK;
     d.octs = d.np / kOctRows;
+    d.duos = d.octs / 2;
     d.blocks = d.np / kBlockRows;
     d.gpw = 128 / g;
     d.gshift = g == 128 ? 3 : (g == 64 ? 2 : 1);
@@ -73,7 +76,8 @@ HLQ_HD int stream_src_byte(int i, int r) { return 2 * ((i >> 1) ^ r) + (i & 1); 
 HLQ_HD int stream_pos_of_src(int b, int r) { return 2 * ((b >> 1) ^ r) + (b & 1); }
 // element offset of meta entry (s, oct, pp, lane, u)
 HLQ_HD int64_t stream_meta_offset(const StreamDims &d, int s, int oct, int pp, int lane, int u) {
-    return ((((int64_t)s * d.octs + oct) * (d.q + 1) + pp) * 32 + lane) * d.gpw + u;
+    const int64_t duo = oct >> 1;
+    return (((((int64_t)s * d.duos + duo) * (d.q + 1) + pp) * 32 + lane) * 2 + (oct & 1)) * d.gpw + u;
 }
 // source group (within the lane's 128 channels) of positional sub-group u for row r
 HLQ_HD int stream_src_group(const StreamDims &d, int u, int r) { return u ^ (r >> d.gshift); }

@@ -181,6 +181,71 @@ def linear_forward(x: torch.Tensor, weight: HLQWeight, workspace: Workspace,
     return out.reshape(*lead, n)
 
 
+class HLQGroup:
+    """Several independent quantized linears run as one persistent kernel launch
+    (hlq_group_*): e.g. the q/k/v projections of a layer, or gate and up."""
+
+    def __init__(self, weights, max_m: int = 1):
+        self.weights = list(weights)          # keeps the handles alive
+        arr = (ctypes.c_void_p * len(self.weights))(*[w.handle.value for w in self.weights])
+        out = ctypes.c_void_p()
+        self.device = self.weights[0].device
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().hlq_group_create(ctypes.byref(out), len(self.weights), arr, max_m),
+                       "hlq_group_create")
+        self._h = out
+        self.max_m = max_m
+        self._bound = None
+
+    def bind(self, xs, ys):
+        """xs[i]: [m, k_i] fp16/bf16 CUDA tensors; ys[i]: [m, n_i] outputs (one dtype each)."""
+        if len(xs) != len(self.weights) or len(ys) != len(self.weights):
+            raise ValueError("one x and one y per member")
+        for x, y, w in zip(xs, ys, self.weights):
+            if x.shape[-1] != w.info.in_channel or y.shape[-1] != w.info.out_channel:
+                raise ValueError("x/y do not match the member's shape")
+            if not (x.is_contiguous() and y.is_contiguous()):
+                raise ValueError("x and y must be contiguous")
+        xa = (ctypes.c_void_p * len(xs))(*[x.data_ptr() for x in xs])
+        ya = (ctypes.c_void_p * len(ys))(*[y.data_ptr() for y in ys])
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().hlq_group_bind(self._h, xa, ya, _DTYPES[xs[0].dtype], _DTYPES[ys[0].dtype],
+                                                 _stream_ptr(self.device)), "hlq_group_bind")
+        self._bound = (list(xs), list(ys))    # keeps the tensors alive
+
+    def forward(self, m: int = 1):
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().hlq_group_forward(self._h, m, _stream_ptr(self.device)), "hlq_group_forward")
+        return self._bound[1]
+
+    def kernel_status(self) -> int:
+        v = ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            _lib.lib().hlq_group_status(self._h, _stream_ptr(self.device), ctypes.byref(v))
+        return v.value
+
+    def info(self):
+        c, sb, ab = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int64()
+        _lib.check(_lib.lib().hlq_group_info(self._h, ctypes.byref(c), ctypes.byref(sb), ctypes.byref(ab)),
+                   "hlq_group_info")
+        return {"count": c.value, "scratch_bytes": sb.value, "algorithmic_bytes": ab.value}
+
+    @property
+    def handle(self):
+        return self._h
+
+    def free(self):
+        if self._h is not None:
+            _lib.lib().hlq_group_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class HLQLinear(torch.nn.Module):
     """Drop-in quantized ``Linear`` over an exported HLQ weight.
 

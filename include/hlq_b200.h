@@ -182,6 +182,31 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
                             void *d_y, int y_dtype, void *d_workspace, size_t workspace_bytes,
                             const hlq_weight *w, void *stream);
 
+/* ---- groups: many independent linears in one launch ----------------------------------- */
+
+/* A group runs the GEMVs of `count` loaded weights (all with the streaming layout, the same
+ * bits and group size, on one device) as ONE persistent kernel launch: the CTAs walk the
+ * concatenated work of all members, so small projections cost no launch of their own.  The
+ * members must be independent: no y may alias an x of the same group.  The group owns its
+ * scratch (per member: completion counters and per-slice partial sums for up to max_m rows,
+ * max_m <= 16) and does not own the weights, which must outlive it.
+ * Replaces the per-projection arm_gemm calls of one decoder layer,
+ * C++/examples/models/llama.cpp:244-675, for projections whose inputs are ready together. */
+typedef struct hlq_group hlq_group;
+int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weights, int max_m);
+/* Set the activation and output pointers of every member (host arrays of `count` device
+ * pointers, x[i] = [m, k_i] 16-byte aligned, y[i] = [m, n_i]); synchronizes `stream`.  The
+ * binding stays until the next call, so that hlq_group_forward is a bare kernel launch. */
+int hlq_group_bind(hlq_group *g, const void *const *d_x, void *const *d_y, int x_dtype,
+                   int y_dtype, void *stream);
+/* y_i[m, n_i] = x_i[m, k_i] . W_hat_i^T + bias_i for every member, m <= max_m. */
+int hlq_group_forward(hlq_group *g, int m, void *stream);
+/* Status word of the group's kernels, as hlq_workspace_status. */
+int hlq_group_status(const hlq_group *g, void *stream, int *kernel_status);
+int hlq_group_info(const hlq_group *g, int *count, int64_t *scratch_bytes,
+                   int64_t *algorithmic_bytes);
+int hlq_group_free(hlq_group *g);
+
 /* ---- diagnostics -------------------------------------------------------------------- */
 
 /* Human-readable text for an hlq_status.  Replaces the reference's exit(-1)/exceptions

@@ -115,9 +115,10 @@ def test_bf16_activations_and_outputs(L):
     assert O.normwise_error(yb, ref) <= TOL_BF16
 
 
-def test_repeated_calls_are_bit_identical(L):
-    """The slice partials are summed in a fixed order, so results do not depend on
-    scheduling; the completion counters return to zero after every call."""
+def test_repeated_calls_agree(L):
+    """The slices of a row are accumulated with fp32 atomics, so repeated calls agree to
+    fp32 rounding (not bit for bit); accumulators and counters return to zero after every
+    call, otherwise the second call would be off by a whole result."""
     d = O.synth_linear(4096, 4096, 2, 128, m=1, seed=0)
     lin, mod = make(d, 128)
     x = torch.from_numpy(d["x"]).cuda()
@@ -125,7 +126,7 @@ def test_repeated_calls_are_bit_identical(L):
     ys = [lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32).clone() for _ in range(5)]
     torch.cuda.synchronize()
     for y in ys[1:]:
-        assert torch.equal(y, ys[0])
+        assert O.normwise_error(y.cpu().numpy(), ys[0].cpu().numpy()) <= 1e-6
     assert mod.workspace.kernel_status() == 0
 
 
@@ -142,15 +143,15 @@ def test_llama_shapes_against_oracle(L, n, k, q, g):
 
 
 def test_size_independent_properties(L):
-    """Exact properties at full size: scaling x by two scales y by two bit-for-bit (fp32
-    out, no bias), zero activations give the bias, and the two independent kernels agree."""
+    """Properties at full size: scaling x by two scales y by two, zero activations give
+    exactly the bias, and the two independent kernels agree."""
     n, k, q, g = 4096, 4096, 2, 128
     d = O.synth_linear(n, k, q, g, m=1, seed=3, bias=False)
     lin, mod = make(d, g)
     _, gen = make(d, g, flags=_lib.HLQ_FLAG_FORCE_EXPORT_LAYOUT)
     y1 = run(mod, d["x"], torch.float32)
     y2 = run(mod, (d["x"].astype(np.float32) * 2).astype(np.float16), torch.float32)
-    assert np.array_equal(y2, 2 * y1)
+    assert O.normwise_error(y2, 2 * y1) <= 1e-6          # exact up to the order of the slice sums
     yg = run(gen, d["x"], torch.float32)
     assert O.normwise_error(yg, y1) <= TOL_F32
     db = O.synth_linear(n, k, q, g, m=1, seed=3, bias=True)
@@ -232,6 +233,55 @@ def test_sharded_weights_reproduce_the_full_product(L):
             got = mod.weight.to_export()
             assert np.array_equal(got.w_quant, want.w_quant)
             assert (got.bias is None) == (r != 0)
+
+
+def test_group_launch_matches_oracle_and_single_launches(L):
+    """Several projections in one persistent launch: same results as one launch each, to
+    fp32 rounding."""
+    lm = linear_mod()
+    shapes = [(256, 1024), (64, 1024), (64, 1024), (1000, 1024), (512, 2560), (40, 512)]
+    for q, g, m in [(2, 128, 1), (3, 64, 3)]:
+        mods, xs, refs = [], [], []
+        for i, (n, k) in enumerate(shapes):
+            d = O.synth_linear(n, k, q, g, m=m, seed=50 + i, bias=(i % 2 == 0), signed_alpha=True)
+            _, mod = make(d, g, max_batch=m)
+            mods.append(mod)
+            xs.append(torch.from_numpy(d["x"]).cuda())
+            refs.append(O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"]))
+        ys = [torch.empty((m, n), dtype=torch.float32, device="cuda") for n, _ in shapes]
+        grp = lm.HLQGroup([mod.weight for mod in mods], max_m=m)
+        grp.bind(xs, ys)
+        for _ in range(3):                      # counters must return to zero between launches
+            grp.forward(m)
+        torch.cuda.synchronize()
+        assert grp.kernel_status() == 0
+        assert grp.info()["count"] == len(shapes)
+        for mod, x, y, ref in zip(mods, xs, ys, refs):
+            assert O.normwise_error(y.cpu().numpy(), ref) <= TOL_F32
+            single = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32)
+            assert O.normwise_error(single.cpu().numpy(), y.cpu().numpy()) <= 1e-6
+        y16 = [torch.empty((m, n), dtype=torch.float16, device="cuda") for n, _ in shapes]
+        grp.bind(xs, y16)
+        grp.forward(m)
+        torch.cuda.synchronize()
+        for y, ref in zip(y16, refs):
+            assert O.normwise_error(y.float().cpu().numpy(), ref) <= TOL_F16
+        with pytest.raises(_lib.HlqError):
+            grp.forward(m + 1)                  # more rows than the group's scratch holds
+
+
+def test_group_rejects_mixed_members(L):
+    lm = linear_mod()
+    a = make(O.synth_linear(64, 512, 2, 128, seed=1), 128)[1]
+    b = make(O.synth_linear(64, 512, 3, 128, seed=1), 128)[1]
+    c = make(O.synth_linear(64, 512, 2, 128, seed=1), 128, flags=_lib.HLQ_FLAG_FORCE_EXPORT_LAYOUT)[1]
+    with pytest.raises(_lib.HlqError):
+        lm.HLQGroup([a.weight, b.weight])
+    with pytest.raises(_lib.HlqError):
+        lm.HLQGroup([a.weight, c.weight])
+    grp = lm.HLQGroup([a.weight])
+    with pytest.raises(_lib.HlqError):
+        grp.forward(1)                          # not bound yet
 
 
 def test_argument_errors(L):

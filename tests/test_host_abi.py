@@ -88,7 +88,9 @@ def emulate_stream_gemv(planes, meta, x, n, k, g, q):
     xp = np.zeros(kp, np.float64)
     xp[:k] = x.astype(np.float64)
     cells = planes.reshape(slices, octs, q, 32, 16)
-    mt = meta.view(np.float16).astype(np.float64).reshape(slices, octs, q + 1, 32, gpw)
+    # scales/zeros are stored two octs (a duo) at a time: [slice][duo][pp][lane][oct & 1][u]
+    mt = meta.view(np.float16).astype(np.float64).reshape(slices, octs // 2, q + 1, 32, 2, gpw)
+    mt = mt.transpose(0, 1, 4, 2, 3, 5).reshape(slices, octs, q + 1, 32, gpw)
     y = np.zeros(np_, np.float64)
     e = np.arange(256)
     bitsel = ((e[:, None] >> np.arange(8)[None, :]) & 1).astype(np.float64)     # [256, 8]
@@ -143,7 +145,7 @@ def test_repack_argument_checks(built_lib):
     assert L.hlq_stream_sizes(64, 512, 128, 5, pb, mb) == 2     # bits
     assert L.hlq_stream_sizes(0, 512, 128, 2, pb, mb) == 1
     assert L.hlq_repack_host(None, None, None, 64, 512, 128, 2, None, None) == 1
-    assert L.hlq_workspace_bytes(1, 4096, 4096, 2, 128) == 256 + 512 + 8 * 4096 * 4
+    assert L.hlq_workspace_bytes(1, 4096, 4096, 2, 128) == 256 + 512 + 4096 * 4
     assert L.hlq_workspace_bytes(0, 4096, 4096, 2, 128) == 0
 
 
