@@ -262,22 +262,31 @@ __device__ __forceinline__ float meta_value(const uint32_t (&m)[GPW], int h) {
 // 16 lookups of one 128-bit word; sums per positional sub-group (16 / GPW bytes each).
 template <int GPW>
 __device__ __forceinline__ void lookup_word(const uint4 &w, const uint32_t (&rt)[8], float (&sum)[GPW]) {
-    float acc[GPW][2];
-#pragma unroll
-    for (int u = 0; u < GPW; ++u) acc[u][0] = acc[u][1] = 0.f;
     const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    constexpr int kWordsPerSub = 4 / GPW;   // 32-bit words per sub-group: 4, 2 or 1
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-        const uint32_t word = words[wi];
-        constexpr int kPerSub = 16 / GPW;
-        const int u0 = (4 * wi) / kPerSub;  // the four bytes of a word share a sub-group
-        acc[u0][0] += lds_f32(byte_into_base<0>(word, rt[2 * wi]));
-        acc[u0][1] += lds_f32_hi(byte_into_base<1>(word, rt[2 * wi]));
-        acc[u0][0] += lds_f32(byte_into_base<2>(word, rt[2 * wi + 1]));
-        acc[u0][1] += lds_f32_hi(byte_into_base<3>(word, rt[2 * wi + 1]));
+    for (int u = 0; u < GPW; ++u) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int q = 0; q < kWordsPerSub; ++q) {
+            const int wi = u * kWordsPerSub + q;
+            const uint32_t word = words[wi];
+            const float v0 = lds_f32(byte_into_base<0>(word, rt[2 * wi]));
+            const float v1 = lds_f32_hi(byte_into_base<1>(word, rt[2 * wi]));
+            const float v2 = lds_f32(byte_into_base<2>(word, rt[2 * wi + 1]));
+            const float v3 = lds_f32_hi(byte_into_base<3>(word, rt[2 * wi + 1]));
+            if (q == 0) {
+                a0 = v0 + v2;
+                a1 = v1 + v3;
+            } else {
+                a0 += v0;
+                a1 += v1;
+                a0 += v2;
+                a1 += v3;
+            }
+        }
+        sum[u] = a0 + a1;
     }
-#pragma unroll
-    for (int u = 0; u < GPW; ++u) sum[u] = acc[u][0] + acc[u][1];
 }
 
 // One duo: both octs' totals, the 4-lane reduction, and the add into the row's fp32
