@@ -929,7 +929,87 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
     return HLQ_OK;
 }
 
+// ---- forward without any allocation: scratch in a fixed device array -------------------------
+//
+// Some callers may not allocate device memory around a forward call: a serving process that
+// handed all of HBM to its own cache manager at start-up has nothing left to cudaMalloc from,
+// and a latency-critical section cannot afford the device-wide synchronization cudaMalloc and
+// cudaFree imply.  For them the LUT GEMV can keep its scratch (status word, completion
+// counters, fp32 row accumulators) in the array below instead of a caller-provided workspace.
+// Every GPU that loads this library holds the array until the process exits.
+constexpr size_t kStaticScratchBytes = 1u << 20;   // 1 MiB, must match HLQ_STATIC_SCRATCH_BYTES
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address.
+// The address is looked up once per device, with that device current.
+static int static_scratch_address(int device, void **out) {
+    static void *addr[64] = {};
+    static bool have[64] = {};
+    if (device < 0 || device >= 64) return HLQ_ERR_INVALID_ARGUMENT;
+    if (!have[device]) {
+        void *p = nullptr;
+        HLQ_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) return HLQ_ERR_CUDA;
+        addr[device] = p;
+        have[device] = true;
+    }
+    *out = addr[device];
+    return HLQ_OK;
+}
+
+int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dtype, void *y,
+                            int y_dtype, cudaStream_t stream) {
+    if (w->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
+    if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return HLQ_ERR_ALIGNMENT;
+    const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
+    const size_t need = workspace_bytes_for(m, d);
+    if (need > kStaticScratchBytes) return HLQ_ERR_WORKSPACE;   // beyond the fixed maximum
+    DeviceInfo *di;
+    int rc = device_info(w->device, &di);
+    if (rc) return rc;
+    if ((uint32_t)di->max_dyn_smem < kLut8DynSmem) return HLQ_ERR_NO_DEVICE;
+    void *scratch = nullptr;
+    rc = static_scratch_address(w->device, &scratch);
+    if (rc) return rc;
+
+    const size_t xsz = 2, ysz = y_dtype == HLQ_F32 ? 4 : 2;
+    for (int m0 = 0; m0 < m; m0 += kLutMaxM) {
+        const int mc = (m - m0) < kLutMaxM ? (m - m0) : kLutMaxM;
+        // The array keeps whatever the previous call left; counters and accumulators must
+        // start at zero, so clear the part this launch uses (a memset node, no allocation).
+        HLQ_CUDA(cudaMemsetAsync(scratch, 0, workspace_bytes_for(mc, d), stream));
+        const Workspace ws = carve_workspace(scratch, mc, d);
+        GemvArgs a = {};
+        a.jobs = nullptr;
+        a.njobs = 0;
+        a.total_units = (long long)d.slices * d.duos;
+        a.status = ws.status;
+        a.dyn_smem = kLut8DynSmem;
+        fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
+                 (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
+        int ctas = di->sms;
+        if (a.total_units < ctas) ctas = (int)a.total_units;
+        rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream);
+        if (rc) return rc;
+    }
+    return HLQ_OK;
+}
+
 }  // namespace hlq
+
+extern "C" int hlq_linear_forward_static(int m, int k, int n, const void *d_x, int x_dtype, void *d_y,
+                                         int y_dtype, const hlq_weight *w, void *stream) {
+    if (!w || m < 0) return HLQ_ERR_INVALID_ARGUMENT;
+    if (k != w->k || n != w->n) return HLQ_ERR_SHAPE;
+    if (m == 0) return HLQ_OK;
+    if (!d_x || !d_y) return HLQ_ERR_INVALID_ARGUMENT;
+    if (y_dtype != HLQ_F16 && y_dtype != HLQ_BF16 && y_dtype != HLQ_F32) return HLQ_ERR_UNSUPPORTED;
+    int cur = -1;
+    HLQ_CUDA(cudaGetDevice(&cur));
+    if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;   // the weight's device must be current
+    return hlq::launch_lut8_gemv_static(w, m, d_x, x_dtype, d_y, y_dtype, (cudaStream_t)stream);
+}
 
 // ---- groups: many independent linears in one persistent launch -----------------------------
 struct hlq_group {

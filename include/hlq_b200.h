@@ -182,6 +182,28 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
                             void *d_y, int y_dtype, void *d_workspace, size_t workspace_bytes,
                             const hlq_weight *w, void *stream);
 
+/* The same product as hlq_linear_forward for a weight in the streaming layout, for callers
+ * that must not allocate device memory around the call and therefore have no workspace to
+ * pass: a serving process whose own memory manager took all of HBM at start-up, or a
+ * latency-critical section that cannot tolerate the device-wide synchronization of
+ * cudaMalloc/cudaFree.  The scratch (status word, completion counters, fp32 accumulators)
+ * lives in a fixed HLQ_STATIC_SCRATCH_BYTES array inside the library, which every GPU that
+ * loads the library holds until the process exits.  The call allocates nothing.
+ *  - Limit: problems whose hlq_workspace_bytes(m, k, n, bits, g) exceeds
+ *    HLQ_STATIC_SCRATCH_BYTES are rejected with HLQ_ERR_WORKSPACE (m = 1: n up to ~250 000
+ *    rows; m = 16: n up to ~16 000).  Weights in the exported layout: HLQ_ERR_UNSUPPORTED.
+ *  - The first call on a device looks the array's address up (with the weight's device
+ *    current, as for hlq_linear_forward); make that first call before any stream capture.
+ *  - All calls on a device share the one array.  Each call clears the part it uses on
+ *    `stream` before its kernel, so leftovers of earlier calls do not matter, but two calls
+ *    whose work overlaps on the GPU (different streams) race on it: keep them on one stream
+ *    or order them with events.
+ * This entry point has no counterpart in the reference (its CPU operator gets its
+ * temp_workplace from the caller, arm_gemm.h:4-14). */
+#define HLQ_STATIC_SCRATCH_BYTES (1u << 20)
+int hlq_linear_forward_static(int m, int k, int n, const void *d_x, int x_dtype, void *d_y,
+                              int y_dtype, const hlq_weight *w, void *stream);
+
 /* ---- groups: many independent linears in one launch ----------------------------------- */
 
 /* A group runs the GEMVs of `count` loaded weights (all with the streaming layout, the same
