@@ -349,8 +349,10 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
     HLQ_CUDA(cudaGetDevice(&cur));
     if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;
     if (impl == 0) {
+        // exported layout -> generic kernel; up to 16 rows -> LUT GEMV (one pass per row);
+        // more rows -> dequantize + tensor-core GEMM
         if (w->layout == HLQ_LAYOUT_EXPORT) impl = 2;
-        else impl = 1;
+        else impl = m <= kLutMaxM ? 1 : 3;
     }
     switch (impl) {
         case 1: return launch_lut8_gemv(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream);

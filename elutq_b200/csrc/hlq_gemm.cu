@@ -1,11 +1,492 @@
-// Dequantize + tensor-core GEMM for prefill (m >= 64).  Placeholder until the tcgen05 kernel
-// lands: reports HLQ_ERR_UNSUPPORTED so that callers fail loudly instead of silently taking
-// another path.
+// Dequantize + tensor-core GEMM over HLQ weights for prefill (m >= 64), sm_100a.
+//
+// Replaces the reference's prefill path, which runs one GEMV per token and re-streams all
+// weights m times (C++/ops/src/arm/arm_gemm.cpp:362-387).  Here a CTA owns a tile of 128
+// output rows x 256 tokens and walks K in steps of 64 channels:
+//   warp 0      TMA producer: the 256 x 64 activation tile of every K step, tensor map with
+//               128-byte swizzle, mbarrier completion (cp.async.bulk.tensor.2d);
+//   warps 4..   dequantizers: two threads per weight row of the tile.  Each reads 4 bytes of
+//               each bit-plane from the streaming layout, turns every bit into a 16-bit mask
+//               through a 16-entry (nibble) shared-memory table that is free of bank conflicts, forms z + sum_p (mask & alpha_p) in
+//               packed fp16 and writes its 64 values as one 128-byte row of the K-major,
+//               128-byte-swizzled operand tile; fence.proxy.async + mbarrier arrive;
+//   warp 1      MMA issuer: one thread issues four tcgen05.mma (128 x 256 x 16, kind::f16,
+//               fp32 accumulator in tensor memory) per K step and commits to the stage's
+//               "empty" mbarrier;
+//   warps 4..7  epilogue: tcgen05.ld of the 128 x 256 fp32 accumulator (one TMEM lane = one
+//               output row), add the bias, store y[token][row].
+// D = W_tile . X_tile^T, i.e. the accumulator is y transposed.
+//
+// Precision: the weights are rounded to fp16 (rel. 2^-11) before the product and
+// accumulation is fp32.  kind::f16 wants both operands in one 16-bit format (a descriptor
+// with fp16 weights and bf16 activations is an illegal instruction on B200), and bf16 weights
+// would carry a rel. 2^-9 rounding, so bf16 activations are first converted to fp16
+// (saturating at +-65504) by a small kernel into the workspace.
+// All mbarrier waits are bounded; on expiry the CTA sets the status word and carries on to
+// its exit so that tensor memory is always released.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
 #include "hlq_internal.h"
 
 namespace hlq {
-int launch_dequant_gemm(const hlq_weight *, int, const void *, int, void *, int, void *, size_t,
-                        cudaStream_t) {
-    return HLQ_ERR_UNSUPPORTED;
+namespace gemm {
+
+constexpr int kTileK = 64;        // channels per K step: 128 bytes of 16-bit operands
+constexpr int kMaxTileM = 256;    // tokens per CTA at most (UMMA N)
+constexpr uint32_t kXBytes = kMaxTileM * kTileK * 2;   // 32 KB reserved per stage
+constexpr uint32_t kLutBytes = 256 * 16;
+constexpr uint32_t kBarBytes = 256;
+constexpr int kSpinLimit = 1 << 24;
+
+template <int ROWS>
+struct Cfg {
+    static constexpr int kAcc = ROWS / 128;                       // accumulators of 128 rows
+    static constexpr int kDeqWarps = ROWS / 16;                   // two threads per weight row
+    static constexpr int kThreads = 128 + 32 * kDeqWarps;         // 4 service warps + dequantizers
+    static constexpr uint32_t kWBytes = ROWS * kTileK * 2;
+    static constexpr uint32_t kStageBytes = kWBytes + kXBytes;
+    static constexpr int kStages = ROWS == 128 ? 4 : 3;           // 192 KB of operand tiles either way
+    static constexpr uint32_t kDynSmem = 1024 + kStages * kStageBytes + kLutBytes + kBarBytes;
+    static constexpr uint32_t kTmemCols = 256 * kAcc;
+};
+
+struct GemmArgs {
+    const uint8_t *planes;
+    const uint16_t *meta;
+    const uint16_t *bias;
+    void *y;
+    int *status;
+    int m, n, k, np, kp, octs, duos, gpw, gshift;
+    int tile_m;          // tokens per CTA: multiple of 32, <= 256
+    int y_dtype;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
+    for (int i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(mbar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row atoms of 1024 bytes.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride between 8-row atoms
+    d |= (uint64_t)1 << 46;                        // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+// kind::f16 instruction descriptor: fp32 accumulator, A and B fp16, both K-major, M = 128,
+// N = tokens per tile.
+__device__ __forceinline__ uint32_t umma_idesc(int tile_m) {
+    return (1u << 4) | ((uint32_t)(tile_m >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar)
+                 : "memory");
+}
+
+// What a dequantizer thread fetches for one K step: the 4 bytes per plane that hold its 32
+// channels of its row, and the fp16 scales / zero of the group they fall into.
+template <int Q>
+struct Raw {
+    uint32_t w[Q];
+    uint16_t al[Q];
+    uint16_t z;
+};
+
+// hh = which 32-channel half of the 64-channel K step this thread owns
+template <int Q>
+__device__ __forceinline__ void load_raw(Raw<Q> &rw, const GemmArgs &a, int kt, int oct, int r, int hh,
+                                         bool row_ok) {
+    const int k0 = kt * kTileK;
+    const int sl = k0 >> 9, j = (k0 >> 7) & 3, h = (k0 >> 6) & 1;
+    const int ln = r * 4 + j;
+    const int half = h ^ (r >> 2);            // which 8 bytes of the lane word hold the 64 channels
+    const int word = hh ^ ((r & 3) >> 1);     // and which 4 of those hold this thread's two byte pairs
+#pragma unroll
+    for (int p = 0; p < Q; ++p) {
+        rw.w[p] = 0u;
+        if (row_ok)
+            rw.w[p] = __ldg((const uint32_t *)(a.planes + (((int64_t)sl * a.octs + oct) * Q + p) * kCellBytes +
+                                               ln * 16 + 8 * half + 4 * word));
+    }
+    // source sub-group inside the lane's 128 channels: g = 128 -> 0, g = 64 -> h, g = 32 -> 2h + hh
+    const int su = a.gpw == 1 ? 0 : (a.gpw == 2 ? h : 2 * h + hh);
+    const int u = su ^ (r >> a.gshift);
+    const int64_t mbase = ((((int64_t)sl * a.duos + (oct >> 1)) * (Q + 1)) * 32 + ln) * 2 * a.gpw +
+                          (oct & 1) * a.gpw + u;
+    const int64_t pstride = (int64_t)32 * 2 * a.gpw;
+#pragma unroll
+    for (int p = 0; p < Q; ++p) rw.al[p] = row_ok ? __ldg(a.meta + mbase + p * pstride) : (uint16_t)0;
+    rw.z = row_ok ? __ldg(a.meta + mbase + Q * pstride) : (uint16_t)0;
+}
+
+template <int ROWS, int Q>
+__global__ void __launch_bounds__(Cfg<ROWS>::kThreads, 1)
+dequant_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
+    using C = Cfg<ROWS>;
+    constexpr int kStages = C::kStages;
+    constexpr uint32_t kStageBytes = C::kStageBytes, kWBytes = C::kWBytes;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t sbase = smem_u32(smem_raw);
+    const uint32_t tiles = (sbase + 1023u) & ~1023u;          // operand tiles need 1024-byte alignment
+    unsigned char *tiles_ptr = smem_raw + (tiles - sbase);
+    const uint32_t lut_u32 = tiles + kStages * kStageBytes;
+    uint2 *lut = (uint2 *)(tiles_ptr + kStages * kStageBytes);
+    const uint32_t bars = lut_u32 + kLutBytes;
+    // barriers: full_x[s], full_w[s], empty[s], acc_full; then the TMEM base and the fail flag
+    const uint32_t bar_full_x = bars, bar_full_w = bars + 8 * kStages, bar_empty = bars + 16 * kStages;
+    const uint32_t bar_acc = bars + 24 * kStages;
+    uint32_t *tmem_slot = (uint32_t *)(tiles_ptr + kStages * kStageBytes + kLutBytes + 24 * kStages + 8);
+    int *fail = (int *)(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * ROWS, m0 = blockIdx.y * a.tile_m;
+    const int ksteps = a.kp / kTileK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full_x + 8 * s, 1);
+            mbar_init(bar_full_w + 8 * s, C::kDeqWarps);   // one arrival per dequantizer warp
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *fail = 0;
+    }
+    if (tid < 16) {
+        // nibble -> four 16-bit masks (two words).  16 entries x 8 bytes = 128 bytes = one row of
+        // all 32 banks: lanes with different nibbles hit different banks, equal nibbles broadcast.
+        const int e = tid;
+        uint2 v;
+        v.x = ((e & 1) ? 0xffffu : 0u) | ((e & 2) ? 0xffff0000u : 0u);
+        v.y = ((e & 4) ? 0xffffu : 0u) | ((e & 8) ? 0xffff0000u : 0u);
+        lut[e] = v;
+    }
+    if (warp == 1) {   // tensor memory: 256 fp32 columns x 128 lanes per accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(C::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer --------------------------------------
+        if (lane == 0) {
+            const uint32_t xbytes = (uint32_t)a.tile_m * kTileK * 2;
+            for (int kt = 0; kt < ksteps; ++kt) {
+                const int s = kt % kStages;
+                if (kt >= kStages && !mbar_wait(bar_empty + 8 * s, ((kt / kStages) - 1) & 1)) *fail = 1;
+                mbar_expect_tx(bar_full_x + 8 * s, xbytes);
+                tma_load_2d(tiles + s * kStageBytes + kWBytes, &xmap, kt * kTileK, m0, bar_full_x + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ----------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(a.tile_m);
+            for (int kt = 0; kt < ksteps; ++kt) {
+                const int s = kt % kStages;
+                const uint32_t ph = (kt / kStages) & 1;
+                if (!mbar_wait(bar_full_x + 8 * s, ph)) *fail = 1;
+                if (!mbar_wait(bar_full_w + 8 * s, ph)) *fail = 1;
+                tc_fence_after();
+                const uint64_t bdesc = umma_desc(tiles + s * kStageBytes + kWBytes);
+#pragma unroll
+                for (int h = 0; h < C::kAcc; ++h) {
+                    const uint64_t adesc = umma_desc(tiles + s * kStageBytes + h * (128 * 128));
+#pragma unroll
+                    for (int kk = 0; kk < kTileK / 16; ++kk)   // 16 channels = 32 bytes = 2 descriptor units
+                        umma_f16(tmem_base + h * 256, adesc + 2 * kk, bdesc + 2 * kk, idesc,
+                                 (kt > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_empty + 8 * s);
+            }
+            umma_commit(bar_acc);
+        }
+    } else if (warp >= 4) {
+        // ------------------------------ dequantizers --------------------------------------
+        // a warp owns 16 rows; lanes 0-15 take channels 0-31 of the K step, lanes 16-31 channels 32-63
+        const int wd = warp - 4;
+        const int t = wd * 16 + (lane & 15);     // weight row inside the tile
+        const int hh = lane >> 4;
+        const int n = n0 + t;
+        const bool row_ok = n < a.np;
+        const int oct = n >> 3, r = n & 7;
+        const bool swap = (r & 1) != 0;          // order of the two byte pairs inside the 4 bytes
+        const uint32_t row_smem = (uint32_t)t * 128u;
+        Raw<Q> cur, nxt;
+        load_raw<Q>(cur, a, 0, oct, r, hh, row_ok);
+        for (int kt = 0; kt < ksteps; ++kt) {
+            const int s = kt % kStages;
+            if (kt + 1 < ksteps) load_raw<Q>(nxt, a, kt + 1, oct, r, hh, row_ok);
+            if (kt >= kStages && !mbar_wait(bar_empty + 8 * s, ((kt / kStages) - 1) & 1)) *fail = 1;
+            uint32_t f[Q][2];                       // [plane][source pair] 16 bits each
+            uint32_t al[Q];                         // fp16x2 alpha per plane
+#pragma unroll
+            for (int p = 0; p < Q; ++p) {
+                const uint32_t lo = cur.w[p] & 0xffffu, hi = cur.w[p] >> 16;
+                f[p][0] = swap ? hi : lo;
+                f[p][1] = swap ? lo : hi;
+                al[p] = (uint32_t)cur.al[p] * 0x10001u;
+            }
+            const uint32_t zz = (uint32_t)cur.z * 0x10001u;
+            const uint32_t wtile = tiles + s * kStageBytes;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {              // source pair: channels 32hh + 16i .. +15
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {          // byte b of the pair: 8 channels = one 16-byte chunk
+                    uint32_t acc[4] = {zz, zz, zz, zz};
+#pragma unroll
+                    for (int p = 0; p < Q; ++p) {
+                        const uint2 mlo = lut[(f[p][i] >> (8 * b)) & 0xfu];
+                        const uint2 mhi = lut[(f[p][i] >> (8 * b + 4)) & 0xfu];
+                        const uint32_t mw[4] = {mlo.x, mlo.y, mhi.x, mhi.y};
+#pragma unroll
+                        for (int w2 = 0; w2 < 4; ++w2) {
+                            const uint32_t term = mw[w2] & al[p];
+                            asm("add.rn.f16x2 %0, %0, %1;" : "+r"(acc[w2]) : "r"(term));
+                        }
+                    }
+                    const int c = 4 * hh + 2 * i + b;  // chunk of the 128-byte row, swizzled by the row
+                    const uint32_t dst = wtile + row_smem + (uint32_t)((c ^ (t & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(acc[0]), "r"(acc[1]),
+                                 "r"(acc[2]), "r"(acc[3]) : "memory");
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full_w + 8 * s);
+            cur = nxt;
+        }
+        // ------------------------------ epilogue ------------------------------------------
+        if (!mbar_wait(bar_acc, 0)) *fail = 1;
+        tc_fence_after();
+        const int q4 = warp & 3;                     // TMEM lanes 32*q4 .. +31 belong to this warp
+        const int hacc = (wd >> 2) % C::kAcc;        // accumulator = 128-row half of the tile
+        const int cpart = wd / (4 * C::kAcc);        // the warps of one (accumulator, quarter) split the tokens
+        const int row = n0 + 128 * hacc + 32 * q4 + lane;
+        float bv = 0.f;
+        if (a.bias && row < a.n) bv = __half2float(__ushort_as_half(a.bias[row]));
+        for (int c0 = 32 * cpart; c0 < a.tile_m; c0 += 64) {
+            uint32_t v[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)(hacc * 256 + c0);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+                  "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+                  "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+                  "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < a.n) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int tok = m0 + c0 + c;
+                    if (tok < a.m) {
+                        const float o = __uint_as_float(v[c]) + bv;
+                        const int64_t idx = (int64_t)tok * a.n + row;
+                        if (a.y_dtype == HLQ_F16) ((__half *)a.y)[idx] = __float2half_rn(o);
+                        else if (a.y_dtype == HLQ_BF16) ((__nv_bfloat16 *)a.y)[idx] = __float2bfloat16_rn(o);
+                        else ((float *)a.y)[idx] = o;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols)
+                     : "memory");
+    }
+    if (tid == 0 && *fail) atomicExch(a.status, 1);
+}
+
+// bf16 -> fp16, eight values per thread and step, saturating instead of overflowing to inf
+__global__ void bf16_to_f16_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, int64_t nvec) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = in[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float lo = __uint_as_float(w[q] << 16), hi = __uint_as_float(w[q] & 0xffff0000u);
+            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(o[q]) : "f"(hi), "f"(lo));
+        }
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+}  // namespace gemm
+
+// Tile shape: rows per CTA (128 or 256) and tokens per CTA (multiple of 32 up to 256), chosen
+// to waste the fewest SM-waves; ties go to the larger tile (less activation traffic from L2).
+static void choose_tiles(int n, int m, int sms, int *rows, int *tile_m) {
+    double best = 1e300;
+    *rows = 128;
+    *tile_m = 256;
+    const int tm_min = m >= 128 ? 128 : ((m + 31) / 32 * 32);
+    for (int r = 256; r >= 128; r -= 128)
+        for (int tm = 256; tm >= tm_min; tm -= 32) {
+            const long long tiles = (long long)((n + r - 1) / r) * ((m + tm - 1) / tm);
+            const long long waves = (tiles + sms - 1) / sms;
+            // 128-row tiles read the activations twice as often per flop: measured ~1.3x slower per flop
+            const double cost = (double)waves * r * tm * (r == 128 ? 1.3 : 1.0);
+            if (cost < best * 0.999) {
+                best = cost;
+                *rows = r;
+                *tile_m = tm;
+            }
+        }
+}
+
+template <int ROWS, int Q>
+static int launch_inst(const gemm::GemmArgs &a, const CUtensorMap &xmap, dim3 grid, cudaStream_t stream) {
+    using C = gemm::Cfg<ROWS>;
+    static bool configured[64] = {};
+    int dev = 0;
+    HLQ_CUDA(cudaGetDevice(&dev));
+    auto kernel = gemm::dequant_gemm_kernel<ROWS, Q>;
+    if (!configured[dev & 63]) {
+        HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kDynSmem));
+        configured[dev & 63] = true;
+    }
+    kernel<<<grid, C::kThreads, C::kDynSmem, stream>>>(a, xmap);
+    count_launch();
+    return note_cuda(cudaGetLastError());
+}
+
+int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
+                        void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    using namespace gemm;
+    if (w->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
+    if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return HLQ_ERR_ALIGNMENT;
+    if (!workspace || workspace_bytes < kWsHeader) return HLQ_ERR_WORKSPACE;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return HLQ_ERR_NO_DEVICE;
+    const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
+    if (x_dtype == HLQ_BF16) {
+        // fp16 copy of the activations behind the workspace header
+        const size_t bytes = (size_t)m * w->k * 2;
+        if (workspace_bytes < kWsHeader + bytes) return HLQ_ERR_WORKSPACE;
+        void *x16 = (char *)workspace + kWsHeader;
+        const int64_t nvec = (int64_t)(bytes / 16);       // k % 8 == 0
+        int64_t blocks = (nvec + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        bf16_to_f16_kernel<<<(int)blocks, 256, 0, stream>>>((const uint4 *)x, (uint4 *)x16, nvec);
+        count_launch();
+        int rc = note_cuda(cudaGetLastError());
+        if (rc) return rc;
+        x = x16;
+    }
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, w->device);
+    int rows = 128, tile_m = 256;
+    choose_tiles(w->n, m, sms, &rows, &tile_m);
+    static const int force_rows = getenv("HLQ_GEMM_ROWS") ? atoi(getenv("HLQ_GEMM_ROWS")) : 0;
+    static const int force_tm = getenv("HLQ_GEMM_TM") ? atoi(getenv("HLQ_GEMM_TM")) : 0;
+    if (force_rows == 128 || force_rows == 256) rows = force_rows;
+    if (force_tm >= 32 && force_tm <= 256 && force_tm % 32 == 0) tile_m = force_tm;
+
+    CUtensorMap xmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)w->k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)w->k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)tile_m};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return HLQ_ERR_INVALID_ARGUMENT;
+
+    GemmArgs a;
+    a.planes = w->d_planes;
+    a.meta = w->d_meta;
+    a.bias = w->d_bias;
+    a.y = y;
+    a.status = (int *)workspace;
+    a.m = m; a.n = w->n; a.k = w->k; a.np = d.np; a.kp = d.kp; a.octs = d.octs; a.duos = d.duos;
+    a.gpw = d.gpw; a.gshift = d.gshift;
+    a.tile_m = tile_m;
+    a.y_dtype = y_dtype;
+    dim3 grid((w->n + rows - 1) / rows, (m + tile_m - 1) / tile_m);
+#define HLQ_GEMM_CASE(R, QV) \
+    if (rows == R && w->q == QV) return launch_inst<R, QV>(a, xmap, grid, stream);
+    HLQ_GEMM_CASE(128, 1) HLQ_GEMM_CASE(128, 2) HLQ_GEMM_CASE(128, 3) HLQ_GEMM_CASE(128, 4)
+    HLQ_GEMM_CASE(256, 1) HLQ_GEMM_CASE(256, 2) HLQ_GEMM_CASE(256, 3) HLQ_GEMM_CASE(256, 4)
+#undef HLQ_GEMM_CASE
+    return HLQ_ERR_SHAPE;
+}
+
 }  // namespace hlq

@@ -789,11 +789,23 @@ __global__ void __launch_bounds__(kGenThreads) lut4_gemv_kernel(const GenArgs a)
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
-size_t workspace_bytes_for(int m, const StreamDims &d) {
+// scratch of the LUT GEMV alone: header, counters, accumulators for up to 16 rows of x
+static size_t lut_scratch_bytes(int m, const StreamDims &d) {
     const int mm = m < kLutMaxM ? m : kLutMaxM;
     size_t counters = ((size_t)mm * d.blocks * sizeof(unsigned) + 255) / 256 * 256;
     size_t partial = (size_t)mm * d.np * sizeof(float);
     return kWsHeader + counters + partial;
+}
+
+size_t workspace_bytes_for(int m, const StreamDims &d) {
+    size_t need = lut_scratch_bytes(m, d);
+    // more rows than the GEMV takes go to the tensor-core GEMM, which may need an fp16 copy
+    // of bf16 activations
+    if (m > kLutMaxM) {
+        const size_t gemm = kWsHeader + (size_t)m * d.k * 2;
+        if (gemm > need) need = gemm;
+    }
+    return need;
 }
 
 Workspace carve_workspace(void *base, int m, const StreamDims &d) {
@@ -902,7 +914,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
     if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return HLQ_ERR_ALIGNMENT;
     const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
-    if (!workspace || workspace_bytes < workspace_bytes_for(m, d)) return HLQ_ERR_WORKSPACE;
+    if (!workspace || workspace_bytes < lut_scratch_bytes(m, d)) return HLQ_ERR_WORKSPACE;
     DeviceInfo *di;
     int rc = device_info(w->device, &di);
     if (rc) return rc;
@@ -963,7 +975,7 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
     if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return HLQ_ERR_ALIGNMENT;
     const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
-    const size_t need = workspace_bytes_for(m, d);
+    const size_t need = lut_scratch_bytes(m, d);
     if (need > kStaticScratchBytes) return HLQ_ERR_WORKSPACE;   // beyond the fixed maximum
     DeviceInfo *di;
     int rc = device_info(w->device, &di);
@@ -978,7 +990,7 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         const int mc = (m - m0) < kLutMaxM ? (m - m0) : kLutMaxM;
         // The array keeps whatever the previous call left; counters and accumulators must
         // start at zero, so clear the part this launch uses (a memset node, no allocation).
-        HLQ_CUDA(cudaMemsetAsync(scratch, 0, workspace_bytes_for(mc, d), stream));
+        HLQ_CUDA(cudaMemsetAsync(scratch, 0, lut_scratch_bytes(mc, d), stream));
         const Workspace ws = carve_workspace(scratch, mc, d);
         GemvArgs a = {};
         a.jobs = nullptr;
