@@ -369,6 +369,68 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """Whole-token decode of a random-init Llama-shaped decoder, tensor-parallel over the
+    ranks (--workload decode).  Reports tokens/s; the linears' algorithmic bytes per token
+    over the step time is given beside it."""
+    import torch
+    import torch.distributed as dist
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    import dataclasses
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = PRESETS[args.model]
+    if args.decode_layers:
+        cfg = dataclasses.replace(cfg, layers=args.decode_layers)
+    cfg = dataclasses.replace(cfg, bits=args.bits, groupsize=args.groupsize)
+    dec = TPDecoder(cfg, dev, rank, world, seed=args.seed, grouped=not args.ungrouped)
+    graph = dec.capture(1)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(args.warmup):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    lb = torch.tensor([float(dec.linear_bytes)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lb, op=dist.ReduceOp.SUM)
+    sec = float(t[0]) / 1e3 / args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_tokens_per_s", "value": 1.0 / sec, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"{args.model} decode, batch 1, context {cfg.ctx}, w{cfg.bits}g{cfg.groupsize}, "
+                                   f"{cfg.layers} layers, tensor-parallel x{world}",
+                       "glue": "PyTorch ops (norm, rope, attention, silu, lm_head) inside one CUDA graph",
+                       "collectives": "NCCL all-reduce after o and down, all-gather of the arg-max"},
+            "linear_algorithmic_bytes_per_token": float(lb[0]),
+            "linear_gbs_over_step_time": float(lb[0]) / sec / 1e9,
+            "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -390,11 +452,17 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture, copied into the roofline object")
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode"])
+    ap.add_argument("--model", default="llama3-70b", help="decoder preset of --workload decode")
+    ap.add_argument("--decode-layers", type=int, default=0, help="override the preset's layer count")
+    ap.add_argument("--ungrouped", action="store_true", help="decode: one launch per projection")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_gpu(args)
 

@@ -1,0 +1,220 @@
+"""Random-init Llama-shaped decoder over HLQ linears, tensor-parallel over the GPUs of one
+node.  It is the caller of the hot path that the reference's `llama::forward` is
+(C++/examples/models/llama.cpp:150-774): per layer RMSNorm, q/k/v, RoPE, KV-cache append,
+single-token attention, o, RMSNorm, gate/up, SiLU*up, down; then the final norm, lm_head and
+argmax.  Only the quantized linears are this package's kernels; the glue runs as PyTorch ops
+(the reference's glue ops are outside the hot path), and the whole step is replayed as one
+CUDA graph.
+
+Tensor parallelism: q/k/v/gate/up are column-parallel (each rank holds whole heads / a slice
+of the ffn), o/down are row-parallel followed by an all-reduce (NCCL), lm_head is
+column-parallel with a local argmax and an all-gather of (value, index).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .format import ExportedLinear
+from .linear import HLQGroup, HLQWeight, Workspace, workspace_bytes
+
+
+@dataclass
+class DecoderConfig:
+    hidden: int
+    ffn: int
+    layers: int
+    n_heads: int
+    n_kv: int
+    head_dim: int
+    vocab: int
+    bits: int = 2
+    groupsize: int = 128
+    ctx: int = 2048
+    rope_theta: float = 500000.0
+
+
+PRESETS = {
+    "llama3-8b": DecoderConfig(4096, 14336, 32, 32, 8, 128, 128256),
+    "llama3-70b": DecoderConfig(8192, 28672, 80, 64, 8, 128, 128256),
+    "tiny": DecoderConfig(1024, 2048, 2, 8, 2, 128, 4096, ctx=256),
+}
+
+
+def _random_export(n, k, q, g, gen, device):
+    wq = torch.randint(0, 256, (q, n, k // 8), dtype=torch.uint8, device=device, generator=gen)
+    ws = (torch.randn((q, n, k // g), device=device, generator=gen) * 0.02).abs().half()
+    wz = (torch.randn((n, k // g), device=device, generator=gen) * 0.01).half()
+    return ExportedLinear(wq, ws, wz, None, g)
+
+
+class TPDecoder:
+    """One decode step (batch 1) at position ctx-1 over a random, already filled KV cache."""
+
+    def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
+                 group=None, seed: int = 0, grouped: bool = True):
+        if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
+            raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
+        self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
+        c = cfg
+        self.hq, self.hkv = c.n_heads // world, c.n_kv // world
+        q_dim, kv_dim = c.n_heads * c.head_dim, c.n_kv * c.head_dim
+        gen = torch.Generator(device=device)
+        rows, cols = _lib.HLQ_SHARD_ROWS, _lib.HLQ_SHARD_COLS
+        self.layers = []
+        self.linear_bytes = 0
+
+        def load(n, k, mode, lseed):
+            gen.manual_seed(lseed)          # every rank draws the full tensor and keeps its shard
+            lin = _random_export(n, k, c.bits, c.groupsize, gen, device)
+            w = HLQWeight.from_export(lin, device=device.index, tp_rank=rank, tp_size=world, shard_mode=mode)
+            self.linear_bytes += w.info.algorithmic_bytes
+            return w
+
+        dt = torch.float16
+        for li in range(c.layers):
+            s0 = seed + li * 16
+            L = {
+                "q": load(q_dim, c.hidden, rows, s0 + 0), "k": load(kv_dim, c.hidden, rows, s0 + 1),
+                "v": load(kv_dim, c.hidden, rows, s0 + 2), "o": load(c.hidden, q_dim, cols, s0 + 3),
+                "gate": load(c.ffn, c.hidden, rows, s0 + 4), "up": load(c.ffn, c.hidden, rows, s0 + 5),
+                "down": load(c.hidden, c.ffn, cols, s0 + 6),
+            }
+            gen.manual_seed(s0 + 7)
+            L["ln1"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
+            L["ln2"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
+            # this rank's KV heads of a random cache filled up to ctx-1
+            kfull = torch.randn((c.n_kv, c.ctx, c.head_dim), device=device, generator=gen).to(dt)
+            vfull = torch.randn((c.n_kv, c.ctx, c.head_dim), device=device, generator=gen).to(dt)
+            L["kc"] = kfull[rank * self.hkv:(rank + 1) * self.hkv].contiguous()
+            L["vc"] = vfull[rank * self.hkv:(rank + 1) * self.hkv].contiguous()
+            del kfull, vfull
+            # buffers
+            L["xn"] = torch.empty((1, c.hidden), dtype=dt, device=device)
+            L["q_o"] = torch.empty((1, self.hq * c.head_dim), dtype=dt, device=device)
+            L["k_o"] = torch.empty((1, self.hkv * c.head_dim), dtype=dt, device=device)
+            L["v_o"] = torch.empty((1, self.hkv * c.head_dim), dtype=dt, device=device)
+            L["att"] = torch.empty((1, self.hq * c.head_dim), dtype=dt, device=device)
+            L["o_o"] = torch.empty((1, c.hidden), dtype=dt, device=device)
+            L["xn2"] = torch.empty((1, c.hidden), dtype=dt, device=device)
+            L["g_o"] = torch.empty((1, c.ffn // world), dtype=dt, device=device)
+            L["u_o"] = torch.empty((1, c.ffn // world), dtype=dt, device=device)
+            L["act"] = torch.empty((1, c.ffn // world), dtype=dt, device=device)
+            L["d_o"] = torch.empty((1, c.hidden), dtype=dt, device=device)
+            if grouped:
+                L["qkv"] = HLQGroup([L["q"], L["k"], L["v"]], max_m=1)
+                L["qkv"].bind([L["xn"]] * 3, [L["q_o"], L["k_o"], L["v_o"]])
+                L["gu"] = HLQGroup([L["gate"], L["up"]], max_m=1)
+                L["gu"].bind([L["xn2"]] * 2, [L["g_o"], L["u_o"]])
+            self.layers.append(L)
+        gen.manual_seed(seed + 100003)
+        self.embed = (torch.randn((c.vocab, c.hidden), device=device, generator=gen) * 0.5).to(dt)
+        self.norm = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
+        vs = c.vocab // world
+        self.lm_head = torch.empty((vs, c.hidden), dtype=dt, device=device)
+        for r0 in range(0, c.vocab, 8192):      # every rank draws all rows, keeps its slice
+            blk = (torch.randn((min(8192, c.vocab - r0), c.hidden), device=device, generator=gen) * 0.02).to(dt)
+            lo, hi = max(r0, rank * vs), min(r0 + blk.shape[0], (rank + 1) * vs)
+            if lo < hi:
+                self.lm_head[lo - rank * vs:hi - rank * vs] = blk[lo - r0:hi - r0]
+        n_max = max(c.hidden, c.ffn // world, q_dim // world)     # scratch grows with the output rows
+        need = workspace_bytes(1, c.hidden, n_max, c.bits, c.groupsize)
+        self.ws = Workspace(need, device)
+        pos = c.ctx - 1
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=device).float() / c.head_dim))
+        ang = pos * inv
+        self.cos, self.sin = torch.cos(ang).to(dt), torch.sin(ang).to(dt)
+        self.pos = pos
+        self.x = torch.empty((1, c.hidden), dtype=dt, device=device)
+        self.logit_max = torch.empty(2 * world, dtype=torch.float32, device=device)
+        self.grouped = grouped
+        self.graph = None
+
+    # ------------------------------------------------------------------------------------
+    def _linear(self, w, x, out):
+        i = w.info
+        st = _lib.lib().hlq_linear_forward(1, i.in_channel, i.out_channel, x.data_ptr(), _lib.HLQ_F16,
+                                           out.data_ptr(), _lib.HLQ_F16, self.ws.ptr, self.ws.nbytes, w.handle,
+                                           torch.cuda.current_stream(self.dev).cuda_stream)
+        _lib.check(st, "hlq_linear_forward")
+
+    def _rope(self, t, heads):
+        c = self.cfg
+        t = t.view(heads, c.head_dim // 2, 2)
+        a, b = t[..., 0], t[..., 1]
+        out = torch.stack((a * self.cos - b * self.sin, a * self.sin + b * self.cos), dim=-1)
+        return out.view(heads, c.head_dim)
+
+    def _all_reduce(self, t):
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+
+    def step_eager(self, token: int):
+        """One decode step; returns the next token id (greedy)."""
+        c = self.cfg
+        x = self.x
+        x.copy_(self.embed[token:token + 1])
+        stream = torch.cuda.current_stream(self.dev).cuda_stream
+        for L in self.layers:
+            L["xn"].copy_(F.rms_norm(x, (c.hidden,), L["ln1"], 1e-5))
+            if self.grouped:
+                _lib.check(_lib.lib().hlq_group_forward(L["qkv"].handle, 1, stream), "hlq_group_forward")
+            else:
+                self._linear(L["q"], L["xn"], L["q_o"])
+                self._linear(L["k"], L["xn"], L["k_o"])
+                self._linear(L["v"], L["xn"], L["v_o"])
+            q = self._rope(L["q_o"], self.hq)
+            k = self._rope(L["k_o"], self.hkv)
+            L["kc"][:, self.pos] = k
+            L["vc"][:, self.pos] = L["v_o"].view(self.hkv, c.head_dim)
+            att = F.scaled_dot_product_attention(q.view(1, self.hq, 1, c.head_dim), L["kc"].unsqueeze(0),
+                                                 L["vc"].unsqueeze(0), enable_gqa=True)
+            L["att"].copy_(att.reshape(1, -1))
+            self._linear(L["o"], L["att"], L["o_o"])
+            self._all_reduce(L["o_o"])
+            x.add_(L["o_o"])
+            L["xn2"].copy_(F.rms_norm(x, (c.hidden,), L["ln2"], 1e-5))
+            if self.grouped:
+                _lib.check(_lib.lib().hlq_group_forward(L["gu"].handle, 1, stream), "hlq_group_forward")
+            else:
+                self._linear(L["gate"], L["xn2"], L["g_o"])
+                self._linear(L["up"], L["xn2"], L["u_o"])
+            torch.mul(F.silu(L["g_o"]), L["u_o"], out=L["act"])
+            self._linear(L["down"], L["act"], L["d_o"])
+            self._all_reduce(L["d_o"])
+            x.add_(L["d_o"])
+        xn = F.rms_norm(x, (c.hidden,), self.norm, 1e-5)
+        logits = torch.matmul(xn, self.lm_head.t()).float()          # this rank's slice of the vocabulary
+        val, idx = logits.max(dim=1)
+        if self.world == 1:
+            self.next_token = idx
+            self.last_logits = logits
+            return idx
+        mine = torch.stack((val[0], (idx[0] + self.rank * (c.vocab // self.world)).float()))
+        parts = self.logit_max.view(self.world, 2)
+        torch.distributed.all_gather_into_tensor(self.logit_max, mine, group=self.group)
+        best = parts[:, 0].argmax()
+        self.next_token = parts[best, 1].long().view(1)
+        self.last_logits = logits
+        return self.next_token
+
+    def capture(self, token: int = 1):
+        """Warm up, then capture one step as a CUDA graph."""
+        s = torch.cuda.Stream(device=self.dev)
+        s.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self.step_eager(token)
+        torch.cuda.current_stream(self.dev).wait_stream(s)
+        torch.cuda.synchronize(self.dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step_eager(token)
+        return self.graph
+
+    def hidden_after_step(self):
+        return self.x

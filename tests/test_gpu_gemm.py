@@ -56,6 +56,27 @@ def test_gemm_matches_oracle(built_lib, q, n, k, g, m, bias):
     assert torch.equal(ya, y32)
 
 
+def test_prefill_shape_of_the_13b_configuration(built_lib):
+    """Llama-2-13B projection at w2g64 with 2048 bf16 tokens; the oracle is evaluated on a
+    random subset of output rows (the full float64 product would take minutes on the CPU)."""
+    from elutq_b200 import linear as lm
+    n, k, q, g, m = 5120, 5120, 2, 64, 2048
+    d = O.synth_linear(n, k, q, g, m=m, seed=13)
+    lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], None, g)
+    mod = lm.HLQLinear.from_exported(lin, device=0, max_batch=m)
+    xb = torch.from_numpy(d["x"].astype(np.float32)).cuda().bfloat16()
+    y = lm.linear_forward(xb, mod.weight, mod.workspace, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert mod.workspace.kernel_status() == 0
+    rows = np.random.default_rng(0).choice(n, size=96, replace=False)
+    ref = O.hlq_linear(xb.float().cpu().numpy(), d["w_quant"][:, rows], d["w_scale"][:, rows],
+                       d["w_zero"][rows], g, dtype=np.float64)
+    assert O.normwise_error(y[:, rows].cpu().numpy(), ref) <= TOL
+    # linearity in the tokens, exact for a power of two
+    y2 = lm.linear_forward(xb * 2, mod.weight, mod.workspace, out_dtype=torch.float32)
+    assert torch.equal(y2, y * 2)
+
+
 def test_gemm_bf16_activations(built_lib):
     from elutq_b200 import linear as lm
     d, mod = build(2, 256, 1024, 64, 128, True, seed=77)

@@ -142,6 +142,17 @@ def test_llama_shapes_against_oracle(L, n, k, q, g):
     assert O.normwise_error(run(mod, d["x"]), ref) <= TOL_F16
 
 
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096)])
+def test_w3g128_batches_at_llama_shapes(L, n, k, m):
+    """Llama-3-8B projections at w3g128 with 1, 4, 8 and 16 rows of activations."""
+    d = O.synth_linear(n, k, 3, 128, m=m, seed=40 + m)
+    lin, mod = make(d, 128, max_batch=m)
+    ref = O.hlq_linear(d["x"].astype(np.float32), d["w_quant"], d["w_scale"], d["w_zero"], 128, dtype=np.float32)
+    assert O.normwise_error(run(mod, d["x"], torch.float32), ref) <= 2e-5
+    assert O.normwise_error(run(mod, d["x"]), ref) <= TOL_F16
+
+
 def test_size_independent_properties(L):
     """Properties at full size: scaling x by two scales y by two, zero activations give
     exactly the bias, and the two independent kernels agree."""

@@ -1,0 +1,78 @@
+"""Tensor-parallel decode on two GPUs against the same decoder on one GPU (NCCL).  Skipped
+where fewer than two GPUs are visible; the sharding logic itself is covered on CPU ranks in
+test_tp_gloo.py and on one GPU in test_gpu_gemv.py."""
+import os
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+import torch.multiprocessing as mp  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, init_file, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world, device_id=dev)
+    try:
+        dec = TPDecoder(PRESETS["tiny"], dev, rank, world, seed=3)
+        dec.step_eager(5)
+        torch.cuda.synchronize()
+        g = dec.capture(5)               # the same step as one CUDA graph, collectives included
+        g.replay()
+        torch.cuda.synchronize()
+        if rank == 0:
+            np.save(os.path.join(out_dir, "x_tp.npy"), dec.hidden_after_step().float().cpu().numpy())
+            np.save(os.path.join(out_dir, "tok_tp.npy"), dec.next_token.cpu().numpy())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_decode_matches_one_gpu():
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    sys.path.insert(0, ROOT)
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker, args=(2, os.path.join(tmp, "init"), tmp), nprocs=2, join=True)
+        x_tp = np.load(os.path.join(tmp, "x_tp.npy"))
+        tok_tp = np.load(os.path.join(tmp, "tok_tp.npy"))
+    dev = torch.device("cuda", 0)
+    one = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=3)
+    one.step_eager(5)
+    torch.cuda.synchronize()
+    x1 = one.hidden_after_step().float().cpu().numpy()
+    # fp16 activations between the layers: the two runs round at different places
+    assert np.abs(x_tp - x1).max() / np.abs(x1).max() <= 1e-2
+    assert int(tok_tp[0]) == int(one.next_token[0])
+
+
+def test_one_gpu_decoder_grouped_equals_ungrouped():
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    sys.path.insert(0, ROOT)
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    dev = torch.device("cuda", 0)
+    a = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=9, grouped=True)
+    b = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=9, grouped=False)
+    a.step_eager(7)
+    b.step_eager(7)
+    torch.cuda.synchronize()
+    xa, xb = a.hidden_after_step().float(), b.hidden_after_step().float()
+    assert (xa - xb).abs().max() / xb.abs().max() <= 2e-3
+    g = a.capture(7)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.isfinite(a.hidden_after_step().float()).all()
