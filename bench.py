@@ -431,6 +431,74 @@ def run_decode(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """Prefill GEMM (--workload prefill): the Llama-2-13B projection set (hidden 5120, ffn 13824)
+    at w2g64 with --tokens bf16 tokens through the dequantize + tcgen05 path.  Reports
+    TFLOP/s (2*m*n*k per projection) over --layers layers of distinct random weights."""
+    import torch
+    from elutq_b200 import _lib
+    from elutq_b200.format import ExportedLinear
+    from elutq_b200.linear import HLQWeight, Workspace, workspace_bytes, linear_forward
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    q, g, m = args.bits, 64, args.tokens
+    hidden, ffn = 5120, 13824
+    shapes = [(hidden, hidden)] * 4 + [(ffn, hidden)] * 2 + [(hidden, ffn)]
+    gen = torch.Generator(device=dev)
+    weights, flops = [], 0.0
+    for layer in range(args.layers):
+        for pi, (n, k) in enumerate(shapes):
+            gen.manual_seed(args.seed + layer * 16 + pi)
+            wq = torch.randint(0, 256, (q, n, k // 8), dtype=torch.uint8, device=dev, generator=gen)
+            ws = (torch.randn((q, n, k // g), device=dev, generator=gen) * 0.02).abs().half()
+            wz = (torch.randn((n, k // g), device=dev, generator=gen) * 0.01).half()
+            weights.append((HLQWeight.from_export(ExportedLinear(wq, ws, wz, None, g), device=local), n, k))
+            flops += 2.0 * m * n * k
+    xs = {k: torch.randn((m, k), device=dev, generator=gen).bfloat16() for k in (hidden, ffn)}
+    ys = {n: torch.empty((m, n), dtype=torch.bfloat16, device=dev) for n in (hidden, ffn)}
+    ws_ = Workspace(max(workspace_bytes(m, k, n, q, g) for _, n, k in weights), dev)
+    L = _lib.lib()
+    before = L.hlq_kernel_launch_count()
+
+    def step():
+        for w, n, k in weights:
+            linear_forward(xs[k], w, ws_, out=ys[n], impl=_lib.IMPL_GEMM)
+    step()
+    launches = L.hlq_kernel_launch_count() - before
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    assert ws_.kernel_status() == 0
+    sec = e0.elapsed_time(e1) / 1e3 / args.steps
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        peak, kind = float(pk["bf16_tflops_sustained"]), "measured, sustained"
+    except Exception:
+        peak, kind = 1400.0, "fallback"
+    tf = flops / sec / 1e12
+    print(json.dumps({
+        "metric": "hlq_prefill_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16 operands (weights dequantized to fp16, bf16 tokens converted), f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": f"llama2-13b projection set w{q}g{g}, {m} bf16 tokens, {args.layers} layers"},
+        "gpu_launches": int(launches * args.steps), "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                     "traffic": None, "peak_source": f"of {kind}", "kernel": "dequant_gemm_kernel"}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -452,7 +520,8 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture, copied into the roofline object")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode"])
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "prefill"])
+    ap.add_argument("--tokens", type=int, default=2048, help="prefill: rows of activations")
     ap.add_argument("--model", default="llama3-70b", help="decoder preset of --workload decode")
     ap.add_argument("--decode-layers", type=int, default=0, help="override the preset's layer count")
     ap.add_argument("--ungrouped", action="store_true", help="decode: one launch per projection")
@@ -463,6 +532,8 @@ def main():
         run_reference(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_gpu(args)
 

@@ -197,8 +197,8 @@ class TPDecoder:
         mine = torch.stack((val[0], (idx[0] + self.rank * (c.vocab // self.world)).float()))
         parts = self.logit_max.view(self.world, 2)
         torch.distributed.all_gather_into_tensor(self.logit_max, mine, group=self.group)
-        best = parts[:, 0].argmax()
-        self.next_token = parts[best, 1].long().view(1)
+        best = parts[:, 0].argmax().view(1)
+        self.next_token = parts[:, 1].gather(0, best).long()      # no host round trip: capturable
         self.last_logits = logits
         return self.next_token
 
