@@ -389,7 +389,8 @@ def run_decode(args):
     if args.decode_layers:
         cfg = dataclasses.replace(cfg, layers=args.decode_layers)
     cfg = dataclasses.replace(cfg, bits=args.bits, groupsize=args.groupsize)
-    dec = TPDecoder(cfg, dev, rank, world, seed=args.seed, grouped=not args.ungrouped)
+    dec = TPDecoder(cfg, dev, rank, world, seed=args.seed, grouped=not args.ungrouped,
+                    fused_allreduce=args.fused_allreduce)
     graph = dec.capture(1)
 
     def barrier():
@@ -422,13 +423,23 @@ def run_decode(args):
             "config": {"workload": f"{args.model} decode, batch 1, context {cfg.ctx}, w{cfg.bits}g{cfg.groupsize}, "
                                    f"{cfg.layers} layers, tensor-parallel x{world}",
                        "glue": "PyTorch ops (norm, rope, attention, silu, lm_head) inside one CUDA graph",
-                       "collectives": "NCCL all-reduce after o and down, all-gather of the arg-max"},
+                       "collectives": ("all-reduce fused into the o and down GEMV kernels (peer stores over NVLink)"
+                                       if args.fused_allreduce else "NCCL all-reduce after o and down")
+                                      + ", NCCL all-gather of the arg-max"},
             "linear_algorithmic_bytes_per_token": float(lb[0]),
             "linear_gbs_over_step_time": float(lb[0]) / sec / 1e9,
             "clocks": clocks}), flush=True)
     if world > 1:
+        # a communicator cannot be torn down while a captured graph still holds its kernels
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        dec.graph = None
+        del graph
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def run_prefill(args):
@@ -525,6 +536,8 @@ def main():
     ap.add_argument("--model", default="llama3-70b", help="decoder preset of --workload decode")
     ap.add_argument("--decode-layers", type=int, default=0, help="override the preset's layer count")
     ap.add_argument("--ungrouped", action="store_true", help="decode: one launch per projection")
+    ap.add_argument("--fused-allreduce", action="store_true",
+                    help="decode: sum the row-parallel outputs inside the GEMV kernel instead of NCCL")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

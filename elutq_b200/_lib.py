@@ -67,6 +67,12 @@ SIGNATURES = {
     "hlq_linear_forward_impl": (c_int, [c_int] * 4 + [c_void_p, c_int, c_void_p, c_int, c_void_p,
                                                       c_size_t, c_void_p, c_void_p]),
     "hlq_linear_forward_static": (c_int, [c_int] * 3 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "hlq_tp_comm_create": (c_int, [POINTER(c_void_p)] + [c_int] * 5),
+    "hlq_tp_comm_handle": (c_int, [c_void_p, c_void_p]),
+    "hlq_tp_comm_connect": (c_int, [c_void_p, c_void_p]),
+    "hlq_tp_comm_free": (c_int, [c_void_p]),
+    "hlq_linear_forward_allreduce": (c_int, [c_int] * 3 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t,
+                                             c_void_p, c_void_p, c_void_p]),
     "hlq_group_create": (c_int, [POINTER(c_void_p), c_int, POINTER(c_void_p), c_int]),
     "hlq_group_bind": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_void_p]),
     "hlq_group_forward": (c_int, [c_void_p, c_int, c_void_p]),

@@ -42,6 +42,8 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <cstring>
+#include <new>
 #include <vector>
 
 #include "hlq_internal.h"
@@ -76,7 +78,18 @@ struct Job {
     long long unit_begin; // first (slice, duo) unit of this job in the launch
 };
 
+// Peer-mapped buffers of a fused all-reduce (one per tensor-parallel communicator), in device
+// memory.  recv[p] is rank p's receive buffer as mapped into this
+// process; slot (parity, source rank, row of x, output row or block).
+struct TpDev {
+    uint2 *recv[8];       // slots of {fp32 bits, launch number}: value and flag travel in one 8-byte store
+    unsigned *seq;        // number of finished fused launches on this rank
+    unsigned *done;       // blocks summed so far in the current launch
+    int rank, world, max_m, np_cap;
+};
+
 struct GemvArgs {
+    const TpDev *tp;      // nullptr: no fused all-reduce
     const Job *jobs;      // njobs descriptors in global memory, or nullptr
     int njobs;            // 0: use `single`
     long long total_units;
@@ -97,6 +110,7 @@ struct Seg {
     int n, np, slices;
     int duo_a, duo_b;
     int x_dtype, y_dtype;
+    int mrow, blocks;
     int live;
 };
 
@@ -107,6 +121,8 @@ constexpr uint32_t kAuxMbarDesc = 2112;  // 2 mbarriers
 constexpr uint32_t kAuxMbarX = 2128;     // 2 mbarriers
 constexpr uint32_t kAuxFlag = 2144;    // int: CTA-wide failure flag
 constexpr uint32_t kAuxSeg = 2304;     // 2 x Seg (<= 128 bytes each)
+constexpr uint32_t kAuxTp = 2560;      // copy of the TpDev of a fused all-reduce (<= 256 bytes)
+static_assert(sizeof(TpDev) <= 256, "TpDev must fit its slot");
 static_assert(sizeof(Seg) <= 128, "Seg must fit its slot");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -149,9 +165,25 @@ __device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
     asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
+__device__ __forceinline__ unsigned ldcg_u32(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ float ldcg_f32(const float *p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+// traffic of the fused all-reduce: one aligned 8-byte store carries a value and the launch
+// number that validates it, so neither side needs a fence (a system-scope fence or release
+// per block costs 5-15 us while the accumulators' reductions are in flight)
+__device__ __forceinline__ void st_relaxed_sys_v2(uint2 *p, uint32_t a, uint32_t b) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ float x_to_float(uint16_t bits, int dtype) {
@@ -376,6 +408,7 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     sg.n = jb.n; sg.np = jb.np; sg.slices = jb.slices;
     sg.duo_a = da; sg.duo_b = db;
     sg.x_dtype = jb.x_dtype; sg.y_dtype = jb.y_dtype;
+    sg.mrow = w.mrow; sg.blocks = jb.blocks;
     sg.live = 1;
     valid = min(kSliceK, jb.k - s * kSliceK);
     w.u += db - da;
@@ -445,14 +478,29 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
             walker_init(wk, a, mrow);
             emit(0);
             emit(1);
-        } else {
-            pdl_wait();   // before this warp's first global write
+        }
+        pdl_wait();       // before this warp's first global write (and before reading `seq`)
+        // fused all-reduce: this launch's number; its parity picks the half of the peer buffers
+        // (the descriptor is copied to shared memory once: it is read for every block)
+        const TpDev *tp = nullptr;
+        unsigned epoch = 0, par = 0;
+        Seg last_sg;
+        last_sg.live = 0;
+        if (a.tp) {
+            uint32_t *dst = (uint32_t *)(aux + kAuxTp);
+            const uint32_t *src = (const uint32_t *)a.tp;
+            for (int i = ftid; i < (int)(sizeof(TpDev) / 4); i += kFinalizers) dst[i] = __ldg(src + i);
+            named_bar_sync<kBarFinalizers, kFinalizers>();
+            tp = (const TpDev *)(aux + kAuxTp);
+            epoch = ldcg_u32(tp->seq) + 1u;
+            par = epoch & 1u;
         }
         for (int i = 0;; ++i) {
             const int slot = i & 1;
             if (!mbar_wait_bounded(mb_desc + 8 * slot, (i >> 1) & 1)) *fail = 1;
             const Seg sg = ring[slot];
             if (!sg.live) break;
+            last_sg = sg;
             named_bar_sync_dyn(kBarSegDone + slot, kThreads);      // consumers are done with it
             named_bar_sync<kBarFinalizers, kFinalizers>();         // every finalizer holds its copy
             if (fw == 0) emit(slot);                               // segment i + 2
@@ -490,15 +538,52 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                     for (int b = 0; b < 8; ++b) {
                         if (rows[b] >= 0) {
                             sg.acc[rows[b]] = 0.f;
-                            if (rows[b] < sg.n) {
-                                float o = v[b];
-                                if (sg.bias) o += __half2float(__ushort_as_half(sg.bias[rows[b]]));
-                                store_y(sg.y, sg.y_base + rows[b], o, sg.y_dtype);
+                            float o = v[b];
+                            if (sg.bias && rows[b] < sg.n) o += __half2float(__ushort_as_half(sg.bias[rows[b]]));
+                            if (!tp) {
+                                if (rows[b] < sg.n) store_y(sg.y, sg.y_base + rows[b], o, sg.y_dtype);
+                            } else {
+                                // push this rank's sum of the block to every rank (itself included)
+                                const long long slot_row =
+                                    (((long long)par * tp->world + tp->rank) * tp->max_m + sg.mrow) * tp->np_cap + rows[b];
+                                for (int p = 0; p < tp->world; ++p)
+                                    st_relaxed_sys_v2(tp->recv[p] + slot_row, __float_as_uint(o), epoch);
                             }
                             if (lane == 0) sg.counters[rows[b] / kBlockRows] = 0;
                         }
                     }
                     mask = mm;
+                }
+            }
+        }
+        if (tp && last_sg.live) {
+            // Second phase of the fused all-reduce.  Pushing never waits; summing is split
+            // statically over the CTAs: poll every rank's slot of a row until it carries this
+            // launch's number, add the ranks' sums in rank order, write y.
+            const Seg &sg = last_sg;
+            const int nwarps = gridDim.x * kFinalWarps;
+            for (int blk = blockIdx.x * kFinalWarps + fw; blk < sg.blocks; blk += nwarps) {
+                const int row = blk * kBlockRows + lane;
+                float sum = 0.f;
+                bool ok = true;
+                for (int src = 0; src < tp->world; ++src) {
+                    const uint2 *slot = tp->recv[tp->rank] +
+                                        (((long long)par * tp->world + src) * tp->max_m + sg.mrow) * tp->np_cap + row;
+                    uint2 v = ld_relaxed_sys_v2(slot);
+                    for (int it = 0; it < kSpinLimit && v.y != epoch; ++it) v = ld_relaxed_sys_v2(slot);
+                    ok = ok && (v.y == epoch);
+                    sum += __uint_as_float(v.x);
+                }
+                if (!ok) *fail = 1;
+                if (row < sg.n) store_y(sg.y, sg.y_base + row, sum, sg.y_dtype);
+                __syncwarp();
+                if (lane == 0) {
+                    const unsigned old = atomicAdd(tp->done, 1u);
+                    if (old + 1u == (unsigned)sg.blocks * gridDim.y) {     // last block of the launch
+                        *tp->done = 0u;
+                        __threadfence();
+                        *tp->seq = epoch;
+                    }
                 }
             }
         }
@@ -1022,6 +1107,139 @@ extern "C" int hlq_linear_forward_static(int m, int k, int n, const void *d_x, i
     if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;   // the weight's device must be current
     return hlq::launch_lut8_gemv_static(w, m, d_x, x_dtype, d_y, y_dtype, (cudaStream_t)stream);
 }
+
+// ---- fused all-reduce for row-parallel linears ----------------------------------------------
+struct hlq_tp_comm {
+    int device = 0, rank = 0, world = 1, max_m = 1, np_cap = 0;
+    unsigned char *local = nullptr;      // this rank's receive buffer, flags, counters (cudaMalloc)
+    size_t bytes = 0, seq_off = 0;
+    void *peer[8] = {};                  // every rank's buffer as mapped here
+    hlq::TpDev *d_tp = nullptr;
+    bool connected = false;
+};
+
+extern "C" {
+
+int hlq_tp_comm_create(hlq_tp_comm **out, int rank, int world, int max_n, int max_m, int device) {
+    if (!out) return HLQ_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || max_n <= 0 || max_m < 1 || max_m > hlq::kLutMaxM)
+        return HLQ_ERR_INVALID_ARGUMENT;
+    hlq_tp_comm *c = new (std::nothrow) hlq_tp_comm();
+    if (!c) return HLQ_ERR_INVALID_ARGUMENT;
+    c->device = device; c->rank = rank; c->world = world; c->max_m = max_m;
+    c->np_cap = (max_n + hlq::kBlockRows - 1) / hlq::kBlockRows * hlq::kBlockRows;
+    const size_t recv = (size_t)2 * world * max_m * c->np_cap * sizeof(uint2);
+    c->seq_off = (recv + 255) / 256 * 256;
+    c->bytes = c->seq_off + 256;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    int rc = HLQ_OK;
+    if (cudaSetDevice(device) != cudaSuccess) rc = HLQ_ERR_NO_DEVICE;
+    if (!rc && cudaMalloc((void **)&c->local, c->bytes) != cudaSuccess) rc = hlq::note_cuda(cudaErrorMemoryAllocation);
+    if (!rc) rc = hlq::note_cuda(cudaMemset(c->local, 0, c->bytes));
+    if (!rc && cudaMalloc((void **)&c->d_tp, sizeof(hlq::TpDev)) != cudaSuccess)
+        rc = hlq::note_cuda(cudaErrorMemoryAllocation);
+    if (prev >= 0) cudaSetDevice(prev);
+    if (rc) {
+        if (c->local) cudaFree(c->local);
+        if (c->d_tp) cudaFree(c->d_tp);
+        delete c;
+        return rc;
+    }
+    *out = c;
+    return HLQ_OK;
+}
+
+int hlq_tp_comm_handle(const hlq_tp_comm *c, void *handle64) {
+    if (!c || !handle64) return HLQ_ERR_INVALID_ARGUMENT;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are exchanged as 64 bytes");
+    cudaIpcMemHandle_t h;
+    HLQ_CUDA(cudaIpcGetMemHandle(&h, c->local));
+    memcpy(handle64, &h, 64);
+    return HLQ_OK;
+}
+
+int hlq_tp_comm_connect(hlq_tp_comm *c, const void *handles) {
+    if (!c || (!handles && c->world > 1)) return HLQ_ERR_INVALID_ARGUMENT;
+    if (c->connected) return HLQ_ERR_INVALID_ARGUMENT;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (cudaSetDevice(c->device) != cudaSuccess) return HLQ_ERR_NO_DEVICE;
+    int rc = HLQ_OK;
+    for (int p = 0; p < c->world && !rc; ++p) {
+        if (p == c->rank) {
+            c->peer[p] = c->local;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + 64 * p, 64);
+        rc = hlq::note_cuda(cudaIpcOpenMemHandle(&c->peer[p], h, cudaIpcMemLazyEnablePeerAccess));
+    }
+    if (!rc) {
+        hlq::TpDev t = {};
+        for (int p = 0; p < c->world; ++p) {
+            t.recv[p] = (uint2 *)c->peer[p];
+        }
+        t.seq = (unsigned *)(c->local + c->seq_off);
+        t.done = t.seq + 1;
+        t.rank = c->rank; t.world = c->world; t.max_m = c->max_m; t.np_cap = c->np_cap;
+        rc = hlq::note_cuda(cudaMemcpy(c->d_tp, &t, sizeof(t), cudaMemcpyHostToDevice));
+    }
+    if (prev >= 0) cudaSetDevice(prev);
+    if (!rc) c->connected = true;
+    return rc;
+}
+
+int hlq_tp_comm_free(hlq_tp_comm *c) {
+    if (!c) return HLQ_OK;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(c->device);
+    for (int p = 0; p < c->world; ++p)
+        if (p != c->rank && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
+    if (c->local) cudaFree(c->local);
+    if (c->d_tp) cudaFree(c->d_tp);
+    if (prev >= 0) cudaSetDevice(prev);
+    delete c;
+    return HLQ_OK;
+}
+
+int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,
+                                 void *d_workspace, size_t workspace_bytes, const hlq_weight *w,
+                                 hlq_tp_comm *comm, void *stream_) {
+    using namespace hlq;
+    if (!w || !comm || m < 0) return HLQ_ERR_INVALID_ARGUMENT;
+    if (k != w->k || n != w->n) return HLQ_ERR_SHAPE;
+    if (m == 0) return HLQ_OK;
+    if (!d_x || !d_y) return HLQ_ERR_INVALID_ARGUMENT;
+    if (!comm->connected || comm->device != w->device) return HLQ_ERR_INVALID_ARGUMENT;
+    if (w->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
+    if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
+    if (y_dtype != HLQ_F16 && y_dtype != HLQ_BF16 && y_dtype != HLQ_F32) return HLQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)d_x & 15) || ((uintptr_t)d_y & 3)) return HLQ_ERR_ALIGNMENT;
+    const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
+    if (d.np > comm->np_cap || m > comm->max_m) return HLQ_ERR_WORKSPACE;
+    if (!d_workspace || workspace_bytes < lut_scratch_bytes(m, d)) return HLQ_ERR_WORKSPACE;
+    int cur = -1;
+    HLQ_CUDA(cudaGetDevice(&cur));
+    if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;
+    DeviceInfo *di;
+    int rc = device_info(w->device, &di);
+    if (rc) return rc;
+    const Workspace ws = carve_workspace(d_workspace, m, d);
+    GemvArgs a = {};
+    a.tp = comm->d_tp;
+    a.total_units = (long long)d.slices * d.duos;
+    a.status = ws.status;
+    a.dyn_smem = kLut8DynSmem;
+    fill_job(a.single, w, d, d_x, x_dtype, d_y, y_dtype, ws.partial, ws.counters, 0);
+    int ctas = di->sms;
+    if (a.total_units < ctas) ctas = (int)a.total_units;
+    return launch_lut8_any(w->q, d.gpw, a, dim3(ctas, m), (cudaStream_t)stream_);
+}
+
+}  // extern "C"
 
 // ---- groups: many independent linears in one persistent launch -----------------------------
 struct hlq_group {

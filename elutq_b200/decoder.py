@@ -56,7 +56,7 @@ class TPDecoder:
     """One decode step (batch 1) at position ctx-1 over a random, already filled KV cache."""
 
     def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
-                 group=None, seed: int = 0, grouped: bool = True):
+                 group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False):
         if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
         self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
@@ -133,6 +133,11 @@ class TPDecoder:
         self.logit_max = torch.empty(2 * world, dtype=torch.float32, device=device)
         self.grouped = grouped
         self.graph = None
+        # all-reduce of o / down inside the GEMV kernel instead of a separate NCCL launch
+        self.comm = None
+        if fused_allreduce and world > 1:
+            from .tp import FusedAllReduceComm
+            self.comm = FusedAllReduceComm(max_n=c.hidden, max_m=1, device=device.index, group=group)
 
     # ------------------------------------------------------------------------------------
     def _linear(self, w, x, out):
@@ -149,9 +154,14 @@ class TPDecoder:
         out = torch.stack((a * self.cos - b * self.sin, a * self.sin + b * self.cos), dim=-1)
         return out.view(heads, c.head_dim)
 
-    def _all_reduce(self, t):
+    def _row_parallel(self, w, x, out):
+        """o / down: this rank's partial product, summed over the ranks."""
+        if self.comm is not None:
+            self.comm.forward(x, w, self.ws, out)
+            return
+        self._linear(w, x, out)
         if self.world > 1:
-            torch.distributed.all_reduce(t, group=self.group)
+            torch.distributed.all_reduce(out, group=self.group)
 
     def step_eager(self, token: int):
         """One decode step; returns the next token id (greedy)."""
@@ -174,8 +184,7 @@ class TPDecoder:
             att = F.scaled_dot_product_attention(q.view(1, self.hq, 1, c.head_dim), L["kc"].unsqueeze(0),
                                                  L["vc"].unsqueeze(0), enable_gqa=True)
             L["att"].copy_(att.reshape(1, -1))
-            self._linear(L["o"], L["att"], L["o_o"])
-            self._all_reduce(L["o_o"])
+            self._row_parallel(L["o"], L["att"], L["o_o"])
             x.add_(L["o_o"])
             L["xn2"].copy_(F.rms_norm(x, (c.hidden,), L["ln2"], 1e-5))
             if self.grouped:
@@ -184,8 +193,7 @@ class TPDecoder:
                 self._linear(L["gate"], L["xn2"], L["g_o"])
                 self._linear(L["up"], L["xn2"], L["u_o"])
             torch.mul(F.silu(L["g_o"]), L["u_o"], out=L["act"])
-            self._linear(L["down"], L["act"], L["d_o"])
-            self._all_reduce(L["d_o"])
+            self._row_parallel(L["down"], L["act"], L["d_o"])
             x.add_(L["d_o"])
         xn = F.rms_norm(x, (c.hidden,), self.norm, 1e-5)
         logits = torch.matmul(xn, self.lm_head.t()).float()          # this rank's slice of the vocabulary

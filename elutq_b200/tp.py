@@ -99,3 +99,54 @@ class RowParallelLinear:
         if self.reduce and self.size > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y
+
+
+class FusedAllReduceComm:
+    """Peer-mapped receive buffers for `hlq_linear_forward_allreduce` (all-reduce fused into the
+    GEMV).  The 64-byte handles travel through ``torch.distributed.all_gather_object``."""
+
+    def __init__(self, max_n: int, max_m: int = 1, device=0, group=None):
+        import ctypes
+        import torch.distributed as dist
+        self.group = group
+        if dist.is_available() and dist.is_initialized():
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        else:
+            self.rank, self.world = 0, 1
+        L = _lib.lib()
+        h = ctypes.c_void_p()
+        _lib.check(L.hlq_tp_comm_create(ctypes.byref(h), self.rank, self.world, max_n, max_m, device),
+                   "hlq_tp_comm_create")
+        self._h = h
+        mine = ctypes.create_string_buffer(64)
+        _lib.check(L.hlq_tp_comm_handle(h, mine), "hlq_tp_comm_handle")
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, mine.raw, group=group)
+        else:
+            handles[0] = mine.raw
+        blob = ctypes.create_string_buffer(b"".join(handles), 64 * self.world)
+        _lib.check(L.hlq_tp_comm_connect(h, blob), "hlq_tp_comm_connect")
+        if self.world > 1:
+            dist.barrier(group=group)          # nobody launches before every mapping exists
+
+    @property
+    def handle(self):
+        return self._h
+
+    def forward(self, x, weight, workspace, out):
+        """out <- sum over ranks of x . W_hat[:, this rank's channels]^T (+ bias of rank 0)."""
+        import torch
+        from .linear import _DTYPES, _stream_ptr
+        i = weight.info
+        m = x.shape[0]
+        st = _lib.lib().hlq_linear_forward_allreduce(
+            m, i.in_channel, i.out_channel, x.data_ptr(), _DTYPES[x.dtype], out.data_ptr(), _DTYPES[out.dtype],
+            workspace.ptr, workspace.nbytes, weight.handle, self._h, _stream_ptr(x.device))
+        _lib.check(st, "hlq_linear_forward_allreduce")
+        return out
+
+    def free(self):
+        if self._h is not None:
+            _lib.lib().hlq_tp_comm_free(self._h)
+            self._h = None

@@ -229,6 +229,31 @@ int hlq_group_info(const hlq_group *g, int *count, int64_t *scratch_bytes,
                    int64_t *algorithmic_bytes);
 int hlq_group_free(hlq_group *g);
 
+/* ---- tensor parallelism: GEMV with the all-reduce fused into its epilogue ---------------- */
+
+/* A communicator owns, on every rank, a receive buffer that all ranks of the node map into
+ * their address space (CUDA IPC over NVLink).  hlq_linear_forward_allreduce runs a
+ * row-parallel (HLQ_SHARD_COLS) linear and sums the ranks' outputs inside the same kernel:
+ * as soon as a rank has finished a block of 32 output rows it stores the block's sums into
+ * every rank's buffer and raises a flag there; at its end every CTA waits (bounded) for the
+ * flags of its share of blocks and adds the ranks' sums in rank order, so all ranks write the
+ * same y.  No separate collective is launched.  Every rank must make the same sequence of
+ * calls on one communicator; one communicator serves one stream.  world <= 8, one process per
+ * GPU.  No counterpart in the reference, which has no multi-device path. */
+typedef struct hlq_tp_comm hlq_tp_comm;
+int hlq_tp_comm_create(hlq_tp_comm **out, int rank, int world, int max_n, int max_m, int device);
+/* 64 opaque bytes that the other ranks need (exchange them with any host-side all-gather). */
+int hlq_tp_comm_handle(const hlq_tp_comm *c, void *handle64);
+/* handles: world x 64 bytes, in rank order (this rank's own entry is ignored). */
+int hlq_tp_comm_connect(hlq_tp_comm *c, const void *handles);
+int hlq_tp_comm_free(hlq_tp_comm *c);
+/* As hlq_linear_forward for m <= max_m rows and a streaming-layout weight; y receives the sum
+ * over all ranks.  A rank that never arrives makes the others give up after a bounded wait
+ * and report through the workspace status word. */
+int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dtype, void *d_y,
+                                 int y_dtype, void *d_workspace, size_t workspace_bytes,
+                                 const hlq_weight *w, hlq_tp_comm *comm, void *stream);
+
 /* ---- diagnostics -------------------------------------------------------------------- */
 
 /* Human-readable text for an hlq_status.  Replaces the reference's exit(-1)/exceptions

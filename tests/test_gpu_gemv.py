@@ -296,6 +296,30 @@ def test_group_rejects_mixed_members(L):
         grp.forward(1)                          # not bound yet
 
 
+def test_fused_allreduce_path_with_one_rank(L):
+    """The GEMV with the all-reduce in its epilogue, world size 1 (push to itself, wait for
+    its own flags, sum one term): same result as the plain GEMV, over several launches so
+    that both halves of the double-buffered slots and the launch counter are exercised."""
+    from elutq_b200 import tp
+    lm = linear_mod()
+    for (q, n, k, g, m) in [(2, 4096, 4096, 128, 1), (3, 200, 1536, 64, 3)]:
+        d = O.synth_linear(n, k, q, g, m=m, seed=60 + n, bias=True, signed_alpha=True)
+        lin, mod = make(d, g, max_batch=m)
+        comm = tp.FusedAllReduceComm(max_n=n, max_m=m, device=0)
+        x = torch.from_numpy(d["x"]).cuda()
+        ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
+        for _ in range(5):
+            y = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+            comm.forward(x, mod.weight, mod.workspace, y)
+            torch.cuda.synchronize()
+            assert mod.workspace.kernel_status() == 0
+            assert O.normwise_error(y.cpu().numpy(), ref) <= TOL_F32
+        with pytest.raises(_lib.HlqError):
+            comm.forward(torch.cat([x, x, x, x, x, x])[: m + 1].contiguous(), mod.weight, mod.workspace,
+                         torch.empty((m + 1, n), dtype=torch.float32, device="cuda"))   # more rows than max_m
+        comm.free()
+
+
 def test_argument_errors(L):
     d = O.synth_linear(64, 512, 2, 128, seed=1)
     lin, mod = make(d, 128)

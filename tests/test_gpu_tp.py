@@ -57,6 +57,55 @@ def test_two_gpu_decode_matches_one_gpu():
     assert int(tok_tp[0]) == int(one.next_token[0])
 
 
+def _fused_worker(rank, world, init_file, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    from elutq_b200 import _lib, format as F, tp
+    from elutq_b200.linear import HLQLinear, linear_forward
+    from oracle import hlq_oracle as O
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world, device_id=dev)
+    try:
+        errs = []
+        for (q, n, k, g, m) in [(2, 4096, 4096, 128, 1), (2, 1000, 2048, 64, 2)]:
+            d = O.synth_linear(n, k, q, g, m=m, seed=21 + n, bias=True, signed_alpha=True)
+            lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], d["bias"], g)
+            mod = HLQLinear.from_exported(lin, device=rank, tp_rank=rank, tp_size=world,
+                                          shard_mode=_lib.HLQ_SHARD_COLS, max_batch=m)
+            comm = tp.FusedAllReduceComm(max_n=n, max_m=m, device=rank)
+            x = torch.from_numpy(tp.shard_activation(d["x"], rank, world, _lib.HLQ_SHARD_COLS).copy()).to(dev)
+            ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
+            y_nccl = linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32)
+            dist.all_reduce(y_nccl)
+            for it in range(6):            # both parities of the slots, several launch numbers
+                y = torch.full((m, n), float("nan"), dtype=torch.float32, device=dev)
+                comm.forward(x, mod.weight, mod.workspace, y)
+                torch.cuda.synchronize()
+                assert mod.workspace.kernel_status() == 0
+                errs.append(O.normwise_error(y.cpu().numpy(), ref))
+                errs.append(O.normwise_error(y.cpu().numpy(), y_nccl.cpu().numpy()))
+            dist.barrier()
+            comm.free()
+        np.save(os.path.join(out_dir, f"fused_{rank}.npy"), np.array(errs))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(150)
+def test_fused_allreduce_matches_nccl_on_two_gpus():
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_fused_worker, args=(2, os.path.join(tmp, "init"), tmp), nprocs=2, join=True)
+        for r in range(2):
+            assert np.load(os.path.join(tmp, f"fused_{r}.npy")).max() <= 1e-5
+
+
 def test_one_gpu_decoder_grouped_equals_ungrouped():
     if not torch.cuda.is_available():
         pytest.fail("needs a CUDA device")
