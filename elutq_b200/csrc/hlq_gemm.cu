@@ -178,6 +178,7 @@ dequant_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) 
     unsigned char *tiles_ptr = smem_raw + (tiles - sbase);
     const uint32_t lut_u32 = tiles + kStages * kStageBytes;
     uint2 *lut = (uint2 *)(tiles_ptr + kStages * kStageBytes);
+    uint32_t *sel_lut = (uint32_t *)(tiles_ptr + kStages * kStageBytes + 128);   // 2 x 16 words
     const uint32_t bars = lut_u32 + kLutBytes;
     // barriers: full_x[s], full_w[s], empty[s], acc_full; then the TMEM base and the fail flag
     const uint32_t bar_full_x = bars, bar_full_w = bars + 8 * kStages, bar_empty = bars + 16 * kStages;
@@ -207,6 +208,17 @@ dequant_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) 
         v.x = ((e & 1) ? 0xffffu : 0u) | ((e & 2) ? 0xffff0000u : 0u);
         v.y = ((e & 4) ? 0xffffu : 0u) | ((e & 8) ? 0xffff0000u : 0u);
         lut[e] = v;
+        // q = 2 only: nibble of plane 0 / plane 1 -> one selector byte per weight for prmt:
+        // byte t = 0x10 + 0x22 * bit_t (plane 0), 0x44 * bit_t (plane 1); their OR selects the
+        // fp16 value of index b0 + 2*b1 out of the 8 bytes {v0, v1, v2, v3}
+        uint32_t sa = 0x10101010u, sb = 0u;
+        for (int t2 = 0; t2 < 4; ++t2)
+            if (e >> t2 & 1) {
+                sa += 0x22u << (8 * t2);
+                sb += 0x44u << (8 * t2);
+            }
+        sel_lut[e] = sa;
+        sel_lut[16 + e] = sb;
     }
     if (warp == 1) {   // tensor memory: 256 fp32 columns x 128 lanes per accumulator
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -270,36 +282,65 @@ dequant_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) 
             if (kt + 1 < ksteps) load_raw<Q>(nxt, a, kt + 1, oct, r, hh, row_ok);
             if (kt >= kStages && !mbar_wait(bar_empty + 8 * s, ((kt / kStages) - 1) & 1)) *fail = 1;
             uint32_t f[Q][2];                       // [plane][source pair] 16 bits each
-            uint32_t al[Q];                         // fp16x2 alpha per plane
 #pragma unroll
             for (int p = 0; p < Q; ++p) {
                 const uint32_t lo = cur.w[p] & 0xffffu, hi = cur.w[p] >> 16;
                 f[p][0] = swap ? hi : lo;
                 f[p][1] = swap ? lo : hi;
-                al[p] = (uint32_t)cur.al[p] * 0x10001u;
             }
-            const uint32_t zz = (uint32_t)cur.z * 0x10001u;
             const uint32_t wtile = tiles + s * kStageBytes;
+            if constexpr (Q == 2) {
+                // the four values a weight of this group can take, each rounded once to fp16
+                const float zf = __half2float(__ushort_as_half(cur.z));
+                const float a0 = __half2float(__ushort_as_half(cur.al[0]));
+                const float a1 = __half2float(__ushort_as_half(cur.al[1]));
+                uint32_t t01, t23;
+                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(t01) : "f"(zf + a0), "f"(zf));
+                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(t23) : "f"(zf + a0 + a1), "f"(zf + a1));
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {              // source pair: channels 32hh + 16i .. +15
+                for (int i = 0; i < 2; ++i) {
 #pragma unroll
-                for (int b = 0; b < 2; ++b) {          // byte b of the pair: 8 channels = one 16-byte chunk
-                    uint32_t acc[4] = {zz, zz, zz, zz};
+                    for (int b = 0; b < 2; ++b) {
+                        uint32_t acc[4];
 #pragma unroll
-                    for (int p = 0; p < Q; ++p) {
-                        const uint2 mlo = lut[(f[p][i] >> (8 * b)) & 0xfu];
-                        const uint2 mhi = lut[(f[p][i] >> (8 * b + 4)) & 0xfu];
-                        const uint32_t mw[4] = {mlo.x, mlo.y, mhi.x, mhi.y};
-#pragma unroll
-                        for (int w2 = 0; w2 < 4; ++w2) {
-                            const uint32_t term = mw[w2] & al[p];
-                            asm("add.rn.f16x2 %0, %0, %1;" : "+r"(acc[w2]) : "r"(term));
+                        for (int hn = 0; hn < 2; ++hn) {       // low / high nibble: 4 weights each
+                            const int sh = 8 * b + 4 * hn;
+                            const uint32_t sel = sel_lut[(f[0][i] >> sh) & 0xfu] | sel_lut[16 + ((f[1][i] >> sh) & 0xfu)];
+                            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(acc[2 * hn]) : "r"(t01), "r"(t23), "r"(sel));
+                            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(acc[2 * hn + 1]) : "r"(t01), "r"(t23), "r"(sel >> 16));
                         }
+                        const int c = 4 * hh + 2 * i + b;
+                        const uint32_t dst = wtile + row_smem + (uint32_t)((c ^ (t & 7)) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(acc[0]), "r"(acc[1]),
+                                     "r"(acc[2]), "r"(acc[3]) : "memory");
                     }
-                    const int c = 4 * hh + 2 * i + b;  // chunk of the 128-byte row, swizzled by the row
-                    const uint32_t dst = wtile + row_smem + (uint32_t)((c ^ (t & 7)) << 4);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(acc[0]), "r"(acc[1]),
-                                 "r"(acc[2]), "r"(acc[3]) : "memory");
+                }
+            } else {
+                uint32_t al[Q];                         // fp16x2 alpha per plane
+#pragma unroll
+                for (int p = 0; p < Q; ++p) al[p] = (uint32_t)cur.al[p] * 0x10001u;
+                const uint32_t zz = (uint32_t)cur.z * 0x10001u;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {              // source pair: channels 32hh + 16i .. +15
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {          // byte b of the pair: 8 channels = one 16-byte chunk
+                        uint32_t acc[4] = {zz, zz, zz, zz};
+#pragma unroll
+                        for (int p = 0; p < Q; ++p) {
+                            const uint2 mlo = lut[(f[p][i] >> (8 * b)) & 0xfu];
+                            const uint2 mhi = lut[(f[p][i] >> (8 * b + 4)) & 0xfu];
+                            const uint32_t mw[4] = {mlo.x, mlo.y, mhi.x, mhi.y};
+#pragma unroll
+                            for (int w2 = 0; w2 < 4; ++w2) {
+                                const uint32_t term = mw[w2] & al[p];
+                                asm("add.rn.f16x2 %0, %0, %1;" : "+r"(acc[w2]) : "r"(term));
+                            }
+                        }
+                        const int c = 4 * hh + 2 * i + b;  // chunk of the 128-byte row, swizzled by the row
+                        const uint32_t dst = wtile + row_smem + (uint32_t)((c ^ (t & 7)) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(acc[0]), "r"(acc[1]),
+                                     "r"(acc[2]), "r"(acc[3]) : "memory");
+                    }
                 }
             }
             fence_proxy_async();
