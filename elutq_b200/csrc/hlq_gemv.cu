@@ -95,6 +95,7 @@ struct GemvArgs {
     long long total_units;
     int *status;
     uint32_t dyn_smem;
+    int seg_cost;         // units charged per (job, slice) when the work is split over the CTAs
     Job single;
 };
 
@@ -353,6 +354,16 @@ __device__ __forceinline__ void compute_tile(const Tile<Q, GPW> &t, const uint32
 }
 
 // ---- control warp: walks the CTA's unit range and emits segment descriptors ---------------
+// The launch's work is split over the CTAs in units of one duo, plus kSegCost units per
+// (job, slice) for what a segment costs beside its duos (the 64 KB of tables, the barriers,
+// the restart of the load ring): CTAs that get many short slices would otherwise finish last.
+// Only launches of several jobs need it (a single job's slices are all alike); there
+// GemvArgs::seg_cost = kSegCost, else 0.
+constexpr int kSegCost = 28;
+__host__ __device__ static inline long long launch_units(int slices, int duos, int seg_cost) {
+    return (long long)slices * (duos + seg_cost);
+}
+
 struct Walker {
     const GemvArgs *a;
     long long u, u_end;
@@ -387,14 +398,27 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     sg.live = 0;
     valid = 0;
     if (w.u >= w.u_end) return nullptr;
-    while (w.u >= w.jb.unit_begin + (long long)w.jb.slices * w.jb.duos && w.jidx + 1 < w.a->njobs) {
+    const int seg_cost = w.a->seg_cost;
+    while (w.u >= w.jb.unit_begin + launch_units(w.jb.slices, w.jb.duos, seg_cost) && w.jidx + 1 < w.a->njobs) {
         ++w.jidx;
         w.jb = w.a->jobs[w.jidx];
     }
     const Job &jb = w.jb;
     const long long local = w.u - jb.unit_begin;
-    const int s = (int)(local / jb.duos);
-    const int da = (int)(local % jb.duos);
+    const int per = jb.duos + seg_cost;
+    const int s = (int)(local / per);
+    int off = (int)(local % per);
+    if (off < seg_cost) {
+        // the range starts in the slice's set-up share: it owns the slice's first duos if it
+        // reaches them, and nothing of this slice otherwise
+        if (w.u + (seg_cost - off) >= w.u_end) {
+            w.u = w.u_end;
+            return nullptr;
+        }
+        w.u += seg_cost - off;
+        off = seg_cost;
+    }
+    const int da = off - seg_cost;
     const long long left = w.u_end - w.u;
     const int db = (int)((long long)(jb.duos - da) < left ? jb.duos : da + left);
     const long long cell = (long long)s * jb.duos + da;           // in duos
@@ -487,6 +511,16 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         Seg last_sg;
         last_sg.live = 0;
         if (a.tp) {
+            // the second phase needs the (single) job's output even in a CTA whose unit range
+            // holds no duo
+            const Job &jb = a.single;
+            last_sg.live = 1;
+            last_sg.y = jb.y;
+            last_sg.y_base = (long long)mrow * jb.n;
+            last_sg.n = jb.n;
+            last_sg.y_dtype = jb.y_dtype;
+            last_sg.mrow = mrow;
+            last_sg.blocks = jb.blocks;
             uint32_t *dst = (uint32_t *)(aux + kAuxTp);
             const uint32_t *src = (const uint32_t *)a.tp;
             for (int i = ftid; i < (int)(sizeof(TpDev) / 4); i += kFinalizers) dst[i] = __ldg(src + i);
@@ -507,17 +541,24 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
             // publish: count finished duos per 32-row block; whoever completes a block sums it
             const int bfirst = sg.duo_a >> 1, blast = (sg.duo_b - 1) >> 1;
             const unsigned total = (unsigned)sg.slices * 2u;
-            for (int b0 = bfirst; b0 <= blast; b0 += kFinalizers) {
-                const int blk = b0 + ftid;
-                bool mine = false;
-                if (blk <= blast) {
-                    const int lo = max(sg.duo_a, 2 * blk), hi = min(sg.duo_b, 2 * blk + 2);
-                    const unsigned cnt = (unsigned)(hi - lo);
-                    __threadfence();
-                    const unsigned old = atomicAdd(&sg.counters[blk], cnt);
-                    mine = (old + cnt == total);
+            constexpr int kPub = 4;      // counter updates a thread keeps in flight
+            for (int b0 = bfirst; b0 <= blast; b0 += kFinalizers * kPub) {
+                unsigned minebits = 0;
+                if (b0 + ftid <= blast) __threadfence();
+#pragma unroll
+                for (int i = 0; i < kPub; ++i) {
+                    const int bi = b0 + i * kFinalizers + ftid;
+                    if (bi <= blast) {
+                        const int lo = max(sg.duo_a, 2 * bi), hi = min(sg.duo_b, 2 * bi + 2);
+                        const unsigned cnt = (unsigned)(hi - lo);
+                        const unsigned old = atomicAdd(&sg.counters[bi], cnt);
+                        minebits |= (old + cnt == total ? 1u : 0u) << i;
+                    }
                 }
-                unsigned mask = __ballot_sync(0xffffffffu, mine);
+#pragma unroll 1
+                for (int i = 0; i < kPub; ++i) {
+                const int blk = b0 + i * kFinalizers + ftid;
+                unsigned mask = __ballot_sync(0xffffffffu, (minebits >> i) & 1u);
                 if (mask) __threadfence();
                 // lane = row of a finished block; several blocks per round trip
                 while (mask) {
@@ -553,6 +594,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                         }
                     }
                     mask = mm;
+                }
                 }
             }
         }
@@ -1013,13 +1055,13 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         GemvArgs a = {};
         a.jobs = nullptr;
         a.njobs = 0;
-        a.total_units = (long long)d.slices * d.duos;
+        a.total_units = launch_units(d.slices, d.duos, 0);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         int ctas = force_ctas > 0 ? force_ctas : di->sms;
-        if (a.total_units < ctas) ctas = (int)a.total_units;
+        if ((long long)d.slices * d.duos < ctas) ctas = d.slices * d.duos;
         rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream);
         if (rc) return rc;
     }
@@ -1080,13 +1122,13 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         GemvArgs a = {};
         a.jobs = nullptr;
         a.njobs = 0;
-        a.total_units = (long long)d.slices * d.duos;
+        a.total_units = launch_units(d.slices, d.duos, 0);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         int ctas = di->sms;
-        if (a.total_units < ctas) ctas = (int)a.total_units;
+        if ((long long)d.slices * d.duos < ctas) ctas = d.slices * d.duos;
         rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream);
         if (rc) return rc;
     }
@@ -1230,12 +1272,12 @@ int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dty
     const Workspace ws = carve_workspace(d_workspace, m, d);
     GemvArgs a = {};
     a.tp = comm->d_tp;
-    a.total_units = (long long)d.slices * d.duos;
+    a.total_units = launch_units(d.slices, d.duos, 0);
     a.status = ws.status;
     a.dyn_smem = kLut8DynSmem;
     fill_job(a.single, w, d, d_x, x_dtype, d_y, y_dtype, ws.partial, ws.counters, 0);
     int ctas = di->sms;
-    if (a.total_units < ctas) ctas = (int)a.total_units;
+    if ((long long)d.slices * d.duos < ctas) ctas = d.slices * d.duos;
     return launch_lut8_any(w->q, d.gpw, a, dim3(ctas, m), (cudaStream_t)stream_);
 }
 
@@ -1246,7 +1288,9 @@ struct hlq_group {
     int device = 0;
     int count = 0, max_m = 1;
     int q = 0, gpw = 0;
-    long long total_units = 0;
+    long long total_units = 0;    // with the per-slice set-up share (launch_units)
+    long long duo_units = 0;      // (slice, duo) pairs
+    int seg_cost = 0;
     std::vector<const hlq_weight *> weights;
     std::vector<hlq::Job> jobs_host;
     hlq::Job *d_jobs = nullptr;
@@ -1302,13 +1346,15 @@ int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weight
         rc = note_cuda(cudaErrorMemoryAllocation);
     if (!rc) rc = note_cuda(cudaMemset(g->d_scratch, 0, off));
     if (!rc) {
+        g->seg_cost = count > 1 ? kSegCost : 0;
         long long ub = 0;
         for (int i = 0; i < count; ++i) {
             const hlq_weight *w = weights[i];
             const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
             fill_job(g->jobs_host[i], w, d, nullptr, HLQ_F16, nullptr, HLQ_F16,
                      (float *)(g->d_scratch + poff[i]), (unsigned *)(g->d_scratch + coff[i]), ub);
-            ub += (long long)d.slices * d.duos;
+            ub += launch_units(d.slices, d.duos, g->seg_cost);
+            g->duo_units += (long long)d.slices * d.duos;
         }
         g->total_units = ub;
     }
@@ -1361,10 +1407,11 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.jobs = g->d_jobs;
     a.njobs = g->count;
     a.total_units = g->total_units;
+    a.seg_cost = g->seg_cost;
     a.status = (int *)g->d_scratch;
     a.dyn_smem = kLut8DynSmem;
     int ctas = force_ctas > 0 ? force_ctas : di->sms;
-    if (a.total_units < ctas) ctas = (int)a.total_units;
+    if (g->duo_units < ctas) ctas = (int)g->duo_units;
     return launch_lut8_any(g->q, g->gpw, a, dim3(ctas, m), (cudaStream_t)stream);
 }
 
