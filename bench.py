@@ -401,7 +401,7 @@ def run_decode(args):
         cfg = dataclasses.replace(cfg, layers=args.decode_layers)
     cfg = dataclasses.replace(cfg, bits=args.bits, groupsize=args.groupsize)
     dec = TPDecoder(cfg, dev, rank, world, seed=args.seed, grouped=not args.ungrouped,
-                    fused_allreduce=args.fused_allreduce)
+                    fused_allreduce=args.fused_allreduce, fused_glue=not args.torch_glue)
     graph = dec.capture(1)
 
     def barrier():
@@ -426,6 +426,22 @@ def run_decode(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(lb, op=dist.ReduceOp.SUM)
     sec = float(t[0]) / 1e3 / args.steps
+    # end to end: the token id comes from pinned host memory and the next token goes back to it
+    tok_in = torch.ones(1, dtype=torch.int64).pin_memory()
+    tok_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        dec.token.copy_(tok_in, non_blocking=True)
+        graph.replay()
+        tok_out.copy_(dec.next_token, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    barrier()
+    t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    sec_e2e = float(t2[0]) / 1e3 / args.steps
     if rank == 0:
         print(json.dumps({
             "metric": "decode_tokens_per_s", "value": 1.0 / sec, "unit": "tokens/s", "n_gpus": world,
@@ -433,10 +449,15 @@ def run_decode(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"{args.model} decode, batch 1, context {cfg.ctx}, w{cfg.bits}g{cfg.groupsize}, "
                                    f"{cfg.layers} layers, tensor-parallel x{world}",
-                       "glue": "PyTorch ops (norm, rope, attention, silu, lm_head) inside one CUDA graph",
+                       "glue": ("PyTorch ops (norm, rope, attention, silu, lm_head) inside one CUDA graph"
+                                if args.torch_glue else
+                                "own kernels (residual+RMSNorm, RoPE+KV append+attention, gated SiLU, argmax), "
+                                "cuBLAS fp16 lm_head, one CUDA graph"),
                        "collectives": ("all-reduce fused into the o and down GEMV kernels (peer stores over NVLink)"
                                        if args.fused_allreduce else "NCCL all-reduce after o and down")
                                       + ", NCCL all-gather of the arg-max"},
+            "e2e": {"value": 1.0 / sec_e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+            "gpu_launches": int(dec.launches_per_step() * args.steps),
             "linear_algorithmic_bytes_per_token": float(lb[0]),
             "linear_gbs_over_step_time": float(lb[0]) / sec / 1e9,
             "clocks": clocks}), flush=True)
@@ -547,6 +568,7 @@ def main():
     ap.add_argument("--model", default="llama3-70b", help="decoder preset of --workload decode")
     ap.add_argument("--decode-layers", type=int, default=0, help="override the preset's layer count")
     ap.add_argument("--ungrouped", action="store_true", help="decode: one launch per projection")
+    ap.add_argument("--torch-glue", action="store_true", help="decode: PyTorch ops between the linears")
     ap.add_argument("--fused-allreduce", action="store_true",
                     help="decode: sum the row-parallel outputs inside the GEMV kernel instead of NCCL")
     args = ap.parse_args()

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_int, c_int64, c_size_t, c_uint, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("HLQ_B200_LIB") or os.path.join(HERE, "csrc", "libhlq_b200.so")
@@ -79,6 +79,12 @@ SIGNATURES = {
     "hlq_group_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
     "hlq_group_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int64), POINTER(c_int64)]),
     "hlq_group_free": (c_int, [c_void_p]),
+    "hlq_rmsnorm": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
+    "hlq_gated_silu": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hlq_argmax": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "hlq_attention_workspace_bytes": (c_size_t, [c_int] * 4),
+    "hlq_rope_cache_attention": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_float, c_float, c_void_p, c_void_p,
+                                                                       c_size_t, c_void_p]),
     "hlq_last_error_string": (c_char_p, [c_int]),
     "hlq_last_cuda_error": (c_int, []),
     "hlq_kernel_launch_count": (c_int64, []),

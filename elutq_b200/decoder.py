@@ -2,9 +2,11 @@
 node.  It is the caller of the hot path that the reference's `llama::forward` is
 (C++/examples/models/llama.cpp:150-774): per layer RMSNorm, q/k/v, RoPE, KV-cache append,
 single-token attention, o, RMSNorm, gate/up, SiLU*up, down; then the final norm, lm_head and
-argmax.  Only the quantized linears are this package's kernels; the glue runs as PyTorch ops
-(the reference's glue ops are outside the hot path), and the whole step is replayed as one
-CUDA graph.
+argmax.  The quantized linears and the glue between them (`glue.py`: residual + RMSNorm,
+RoPE + KV append + attention as one kernel, gated SiLU, argmax) are this package's kernels;
+the embedding row copy and the fp16 lm_head product are library calls.  `fused_glue=False`
+runs the same glue as PyTorch ops instead (the parity reference of the tests).  The whole
+step is replayed as one CUDA graph; the position lives in device memory.
 
 Tensor parallelism: q/k/v/gate/up are column-parallel (each rank holds whole heads / a slice
 of the ffn), o/down are row-parallel followed by an all-reduce (NCCL), lm_head is
@@ -56,7 +58,8 @@ class TPDecoder:
     """One decode step (batch 1) at position ctx-1 over a random, already filled KV cache."""
 
     def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
-                 group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False):
+                 group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False,
+                 fused_glue: bool = True):
         if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
         self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
@@ -87,11 +90,12 @@ class TPDecoder:
             gen.manual_seed(s0 + 7)
             L["ln1"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
             L["ln2"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
-            # this rank's KV heads of a random cache filled up to ctx-1
-            kfull = torch.randn((c.n_kv, c.ctx, c.head_dim), device=device, generator=gen).to(dt)
-            vfull = torch.randn((c.n_kv, c.ctx, c.head_dim), device=device, generator=gen).to(dt)
-            L["kc"] = kfull[rank * self.hkv:(rank + 1) * self.hkv].contiguous()
-            L["vc"] = vfull[rank * self.hkv:(rank + 1) * self.hkv].contiguous()
+            # this rank's KV heads of a random cache filled up to ctx-1, [position][head][dhead]
+            # as the reference keeps it (arm_cache.cpp:17-21)
+            kfull = torch.randn((c.ctx, c.n_kv, c.head_dim), device=device, generator=gen).to(dt)
+            vfull = torch.randn((c.ctx, c.n_kv, c.head_dim), device=device, generator=gen).to(dt)
+            L["kc"] = kfull[:, rank * self.hkv:(rank + 1) * self.hkv].contiguous()
+            L["vc"] = vfull[:, rank * self.hkv:(rank + 1) * self.hkv].contiguous()
             del kfull, vfull
             # buffers
             L["xn"] = torch.empty((1, c.hidden), dtype=dt, device=device)
@@ -127,8 +131,16 @@ class TPDecoder:
         pos = c.ctx - 1
         inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=device).float() / c.head_dim))
         ang = pos * inv
-        self.cos, self.sin = torch.cos(ang).to(dt), torch.sin(ang).to(dt)
+        self.cos, self.sin = torch.cos(ang), torch.sin(ang)
         self.pos = pos
+        self.position = torch.tensor([pos], dtype=torch.int32, device=device)
+        self.token = torch.zeros(1, dtype=torch.int64, device=device)    # input token id (a graph input)
+        self.fused_glue = fused_glue
+        self.next_index = torch.zeros(1, dtype=torch.int32, device=device)
+        self.next_value = torch.zeros(1, dtype=torch.float32, device=device)
+        if fused_glue:
+            from .glue import DecodeAttention
+            self.attn = DecodeAttention(self.hq, self.hkv, c.head_dim, c.ctx, c.rope_theta, device)
         self.x = torch.empty((1, c.hidden), dtype=dt, device=device)
         self.logit_max = torch.empty(2 * world, dtype=torch.float32, device=device)
         self.grouped = grouped
@@ -148,11 +160,11 @@ class TPDecoder:
         _lib.check(st, "hlq_linear_forward")
 
     def _rope(self, t, heads):
+        """Pairs (j, j + dhead/2) as in the reference (arm_rotary.cpp:28-49); fp32 math."""
         c = self.cfg
-        t = t.view(heads, c.head_dim // 2, 2)
-        a, b = t[..., 0], t[..., 1]
-        out = torch.stack((a * self.cos - b * self.sin, a * self.sin + b * self.cos), dim=-1)
-        return out.view(heads, c.head_dim)
+        t = t.view(heads, c.head_dim).float()
+        a, b = t[:, :c.head_dim // 2], t[:, c.head_dim // 2:]
+        return torch.cat((a * self.cos - b * self.sin, a * self.sin + b * self.cos), dim=-1).half()
 
     def _row_parallel(self, w, x, out):
         """o / down: this rank's partial product, summed over the ranks."""
@@ -163,52 +175,106 @@ class TPDecoder:
         if self.world > 1:
             torch.distributed.all_reduce(out, group=self.group)
 
-    def step_eager(self, token: int):
-        """One decode step; returns the next token id (greedy)."""
+    def step_eager(self, token=None):
+        """One decode step on `token` (None: the id already in self.token); returns the next
+        token id (greedy) as a device tensor."""
+        return self._step_fused(token) if self.fused_glue else self._step_torch(token)
+
+    def _groups_or_linears(self, L, which, stream):
+        if self.grouped:
+            _lib.check(_lib.lib().hlq_group_forward(L[which].handle, 1, stream), "hlq_group_forward")
+        elif which == "qkv":
+            self._linear(L["q"], L["xn"], L["q_o"])
+            self._linear(L["k"], L["xn"], L["k_o"])
+            self._linear(L["v"], L["xn"], L["v_o"])
+        else:
+            self._linear(L["gate"], L["xn2"], L["g_o"])
+            self._linear(L["up"], L["xn2"], L["u_o"])
+
+    def _step_fused(self, token):
+        """The glue as this package's kernels: 8 launches per layer.  The residual stream is
+        carried the way the reference's model does (llama.cpp:193-215, 554, 717): each norm
+        first adds the previous linear's output to it."""
+        from . import glue
         c = self.cfg
         x = self.x
-        x.copy_(self.embed[token:token + 1])
+        if token is not None:
+            self.token.fill_(int(token))
+        torch.index_select(self.embed, 0, self.token, out=x)
         stream = torch.cuda.current_stream(self.dev).cuda_stream
+        delta = None
         for L in self.layers:
-            L["xn"].copy_(F.rms_norm(x, (c.hidden,), L["ln1"], 1e-5))
-            if self.grouped:
-                _lib.check(_lib.lib().hlq_group_forward(L["qkv"].handle, 1, stream), "hlq_group_forward")
+            if delta is None:
+                glue.rmsnorm(x, L["ln1"], 1e-5, out=L["xn"])
             else:
-                self._linear(L["q"], L["xn"], L["q_o"])
-                self._linear(L["k"], L["xn"], L["k_o"])
-                self._linear(L["v"], L["xn"], L["v_o"])
-            q = self._rope(L["q_o"], self.hq)
-            k = self._rope(L["k_o"], self.hkv)
-            L["kc"][:, self.pos] = k
-            L["vc"][:, self.pos] = L["v_o"].view(self.hkv, c.head_dim)
-            att = F.scaled_dot_product_attention(q.view(1, self.hq, 1, c.head_dim), L["kc"].unsqueeze(0),
-                                                 L["vc"].unsqueeze(0), enable_gqa=True)
-            L["att"].copy_(att.reshape(1, -1))
+                glue.rmsnorm(delta, L["ln1"], 1e-5, out=L["xn"], residual=x, res_out=x)
+            self._groups_or_linears(L, "qkv", stream)
+            self.attn.forward(L["q_o"].view(self.hq, c.head_dim), L["k_o"].view(self.hkv, c.head_dim),
+                              L["v_o"].view(self.hkv, c.head_dim), L["kc"], L["vc"], self.position,
+                              out=L["att"].view(self.hq, c.head_dim))
             self._row_parallel(L["o"], L["att"], L["o_o"])
-            x.add_(L["o_o"])
-            L["xn2"].copy_(F.rms_norm(x, (c.hidden,), L["ln2"], 1e-5))
-            if self.grouped:
-                _lib.check(_lib.lib().hlq_group_forward(L["gu"].handle, 1, stream), "hlq_group_forward")
-            else:
-                self._linear(L["gate"], L["xn2"], L["g_o"])
-                self._linear(L["up"], L["xn2"], L["u_o"])
-            torch.mul(F.silu(L["g_o"]), L["u_o"], out=L["act"])
+            glue.rmsnorm(L["o_o"], L["ln2"], 1e-5, out=L["xn2"], residual=x, res_out=x)
+            self._groups_or_linears(L, "gu", stream)
+            glue.gated_silu(L["g_o"], L["u_o"], out=L["act"])
             self._row_parallel(L["down"], L["act"], L["d_o"])
-            x.add_(L["d_o"])
-        xn = F.rms_norm(x, (c.hidden,), self.norm, 1e-5)
-        logits = torch.matmul(xn, self.lm_head.t()).float()          # this rank's slice of the vocabulary
-        val, idx = logits.max(dim=1)
+            delta = L["d_o"]
+        xn = self.layers[0]["xn"]
+        glue.rmsnorm(delta, self.norm, 1e-5, out=xn, residual=x, res_out=x)
+        logits = torch.matmul(xn, self.lm_head.t())                  # this rank's slice of the vocabulary (fp16)
+        glue.argmax(logits.view(-1), self.next_index, self.next_value)
+        self.last_logits = logits
+        return self._pick(self.next_value, self.next_index)
+
+    def _pick(self, val, idx):
+        """Greedy token over the ranks' slices: all-gather of (value, global index)."""
+        c = self.cfg
         if self.world == 1:
-            self.next_token = idx
-            self.last_logits = logits
-            return idx
-        mine = torch.stack((val[0], (idx[0] + self.rank * (c.vocab // self.world)).float()))
+            self.next_token = idx.long()
+            return self.next_token
+        mine = torch.stack((val[0].float(), (idx[0] + self.rank * (c.vocab // self.world)).float()))
         parts = self.logit_max.view(self.world, 2)
         torch.distributed.all_gather_into_tensor(self.logit_max, mine, group=self.group)
         best = parts[:, 0].argmax().view(1)
         self.next_token = parts[:, 1].gather(0, best).long()      # no host round trip: capturable
-        self.last_logits = logits
         return self.next_token
+
+    def _step_torch(self, token):
+        """The same step with the glue as PyTorch ops (fp32 math, fp16 storage)."""
+        c = self.cfg
+        x = self.x
+        if token is not None:
+            self.token.fill_(int(token))
+        torch.index_select(self.embed, 0, self.token, out=x)
+        stream = torch.cuda.current_stream(self.dev).cuda_stream
+
+        def norm(t, w):
+            tf = t.float()
+            return (tf * w.float() / torch.sqrt((tf * tf).mean(dim=-1, keepdim=True) + 1e-5)).half()
+
+        for L in self.layers:
+            L["xn"].copy_(norm(x, L["ln1"]))
+            self._groups_or_linears(L, "qkv", stream)
+            q = self._rope(L["q_o"], self.hq)
+            L["kc"][self.pos] = self._rope(L["k_o"], self.hkv)
+            L["vc"][self.pos] = L["v_o"].view(self.hkv, c.head_dim)
+            att = F.scaled_dot_product_attention(q.view(1, self.hq, 1, c.head_dim).float(),
+                                                 L["kc"][:self.pos + 1].permute(1, 0, 2).unsqueeze(0).float(),
+                                                 L["vc"][:self.pos + 1].permute(1, 0, 2).unsqueeze(0).float(),
+                                                 enable_gqa=True)
+            L["att"].copy_(att.reshape(1, -1))
+            self._row_parallel(L["o"], L["att"], L["o_o"])
+            x.add_(L["o_o"])
+            L["xn2"].copy_(norm(x, L["ln2"]))
+            self._groups_or_linears(L, "gu", stream)
+            g = L["g_o"].float()
+            L["act"].copy_(L["u_o"].float() * (g / (1 + torch.exp(-g))))
+            self._row_parallel(L["down"], L["act"], L["d_o"])
+            x.add_(L["d_o"])
+        xn = norm(x, self.norm)
+        logits = torch.matmul(xn, self.lm_head.t())
+        val, idx = logits.float().max(dim=1)
+        self.last_logits = logits
+        return self._pick(val, idx.int())
 
     def capture(self, token: int = 1):
         """Warm up, then capture one step as a CUDA graph."""
@@ -221,8 +287,16 @@ class TPDecoder:
         torch.cuda.synchronize(self.dev)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.step_eager(token)
+            self.step_eager(None)          # the graph reads the token id from self.token
         return self.graph
+
+    def launches_per_step(self) -> int:
+        """Kernels of this package in one step (the embedding copy, the lm_head product and the
+        collectives are library calls and not counted)."""
+        per_layer = (2 if self.grouped else 5) + 2          # qkv, gate/up (+ o, down below)
+        if self.fused_glue:
+            per_layer += 4                                  # two norms, attention, gated silu
+        return len(self.layers) * per_layer + (2 if self.fused_glue else 0)
 
     def hidden_after_step(self):
         return self.x

@@ -254,6 +254,47 @@ int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dty
                                  int y_dtype, void *d_workspace, size_t workspace_bytes,
                                  const hlq_weight *w, hlq_tp_comm *comm, void *stream);
 
+/* ---- decoder glue between the linears (fp16, device pointers, one token) --------------
+ *
+ * The per-token ops the reference's model runs between two quantized linears
+ * (C++/examples/models/llama.cpp:193-215, 396-476, 554, 646, 717, 763).  All pointers are
+ * device pointers to fp16 unless noted, 16-byte aligned; all work is queued on `stream`. */
+
+/* out[r,:] = t * gamma / sqrt(mean(t^2) + eps), t = x[r,:] (+ residual[r,:]).  With a
+ * residual, t is also stored rounded to fp16 in res_out and the rounded value is what gets
+ * normalized.  out may alias x and res_out may alias residual (the reference calls it so).
+ * n % 8 == 0.  Replaces launch_rms_norm / launch_pre_rms_norm
+ * (C++/ops/src/arm/arm_rmsnorm.cpp:165-212; math at :25-41 and :68-85). */
+int hlq_rmsnorm(int rows, int n, const void *d_x, const void *d_residual_or_null,
+                void *d_res_out_or_null, const void *d_gamma, float eps, void *d_out, void *stream);
+
+/* out = up * gate / (1 + exp(-gate)) in fp32, rounded to fp16; rows * n % 8 == 0.  Replaces
+ * gated_silu (C++/ops/src/arm/arm_activation.cpp:22-52, 92-106). */
+int hlq_gated_silu(int rows, int n, const void *d_gate, const void *d_up, void *d_out, void *stream);
+
+/* Index (and optionally value) of the first largest of n values (dtype HLQ_F16 or HLQ_F32).
+ * Replaces arm_argmax_last for one token (C++/ops/src/arm/arm_argmax.cpp:3-29). */
+int hlq_argmax(int n, const void *d_values, int dtype, int *d_index_out, float *d_value_out_or_null,
+               void *stream);
+
+/* One decode step of attention for one token, in one kernel:
+ *   RoPE on q [head_q][dhead] and k [head_kv][dhead] with pairs (j, j + dhead/2) and angle
+ *   position * rotary_base^(-2j/dhead)      (launch_llama_qkv_apply_rotary, arm_rotary.cpp:4-88),
+ *   append of the roped k and of v at `position` into the caches [max_ctx][head_kv][dhead]
+ *                                           (arm_cache, arm_cache.cpp:3-22),
+ *   softmax(scale * q.K) V over positions 0..position with head h reading kv head
+ *   h * head_kv / head_q                    (arm_attention, arm_attention.cpp:196-270, 320-340).
+ * `d_position` points to ONE int in device memory (so a captured graph can be replayed for
+ * the next token after the caller increments it); a position outside [0, max_ctx) is clamped
+ * and reported through the workspace status word (hlq_workspace_status).  dhead 64 or 128,
+ * head_q / head_kv <= 8.  The workspace needs hlq_attention_workspace_bytes(...) bytes, zeroed
+ * once with hlq_workspace_init; one workspace per stream. */
+size_t hlq_attention_workspace_bytes(int head_q, int head_kv, int dhead, int max_ctx);
+int hlq_rope_cache_attention(const void *d_q, const void *d_k, const void *d_v, void *d_kcache,
+                             void *d_vcache, const int *d_position, int head_q, int head_kv,
+                             int dhead, int max_ctx, float rotary_base, float scale, void *d_out,
+                             void *d_workspace, size_t workspace_bytes, void *stream);
+
 /* ---- diagnostics -------------------------------------------------------------------- */
 
 /* Human-readable text for an hlq_status.  Replaces the reference's exit(-1)/exceptions

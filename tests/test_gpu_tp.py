@@ -123,3 +123,34 @@ def test_one_gpu_decoder_grouped_equals_ungrouped():
     g.replay()
     torch.cuda.synchronize()
     assert torch.isfinite(a.hidden_after_step().float()).all()
+
+
+def test_one_gpu_decoder_own_glue_equals_torch_glue():
+    """The step with the package's glue kernels against the same step with PyTorch ops."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    sys.path.insert(0, ROOT)
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    dev = torch.device("cuda", 0)
+    a = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=11, fused_glue=True)
+    b = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=11, fused_glue=False)
+    ta, tb = a.step_eager(7), b.step_eager(7)
+    torch.cuda.synchronize()
+    xa, xb = a.hidden_after_step().float(), b.hidden_after_step().float()
+    assert (xa - xb).abs().max() / xb.abs().max() <= 4e-3
+    la, lb = a.last_logits.float(), b.last_logits.float()
+    assert (la - lb).abs().max() / lb.abs().max() <= 1e-2
+    # the appended cache rows agree too (v bit-exactly)
+    pos = a.pos
+    for La, Lb in zip(a.layers, b.layers):
+        assert torch.equal(La["vc"][pos], Lb["vc"][pos]) or \
+            (La["vc"][pos].float() - Lb["vc"][pos].float()).abs().max() <= 2e-2
+    if int(lb.argmax()) == int(la.argmax()):
+        assert int(ta.item()) == int(tb.item())
+    g = a.capture(7)
+    a.token.fill_(7)
+    g.replay()
+    torch.cuda.synchronize()
+    assert a.attn.status() == 0
+    assert (a.hidden_after_step().float() - xb).abs().max() / xb.abs().max() <= 4e-3
+
