@@ -96,6 +96,8 @@ struct GemvArgs {
     int *status;
     uint32_t dyn_smem;
     int seg_cost;         // units charged per (job, slice) when the work is split over the CTAs
+    int row_base;         // first row of x this launch serves (grid.y passes of R rows follow)
+    int y_is_f32;         // host only: fp32 outputs keep one row per pass (fp32 table entries)
     Job single;
 };
 
@@ -108,7 +110,7 @@ struct Seg {
     unsigned *counters;     // counters of mrow
     void *y;
     long long y_base;       // element offset of mrow in y
-    int n, np, slices;
+    int n, np, slices, k;
     int duo_a, duo_b;
     int x_dtype, y_dtype;
     int mrow, blocks;
@@ -123,6 +125,8 @@ constexpr uint32_t kAuxMbarX = 2128;     // 2 mbarriers
 constexpr uint32_t kAuxFlag = 2144;    // int: CTA-wide failure flag
 constexpr uint32_t kAuxSeg = 2304;     // 2 x Seg (<= 128 bytes each)
 constexpr uint32_t kAuxTp = 2560;      // copy of the TpDev of a fused all-reduce (<= 256 bytes)
+constexpr uint32_t kAuxXsum2 = 2816;   // two-row passes: 2 x 16 group sums
+constexpr uint32_t kAuxX2 = 4096;      // two-row passes: 2 slots x 2 rows x 512 activations
 static_assert(sizeof(TpDev) <= 256, "TpDev must fit its slot");
 static_assert(sizeof(Seg) <= 128, "Seg must fit its slot");
 
@@ -138,6 +142,19 @@ __device__ __forceinline__ float lds_f32_hi(uint32_t addr) {   // second bank-ro
     float v;
     asm volatile("ld.shared.f32 %0, [%1+128];" : "=f"(v) : "r"(addr));
     return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32_hi(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+128];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
@@ -322,6 +339,78 @@ __device__ __forceinline__ void lookup_word(const uint4 &w, const uint32_t (&rt)
     }
 }
 
+// Two rows of x at once: a table entry is a half2 {row 0, row 1} of the same subset sum, so one
+// lookup serves both rows (entries are rounded to fp16 as the reference's tables are; the sums
+// are taken in fp32).
+template <int GPW>
+__device__ __forceinline__ void lookup_word2(const uint4 &w, const uint32_t (&rt)[8], float (&s0)[GPW],
+                                             float (&s1)[GPW]) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    constexpr int kWordsPerSub = 4 / GPW;
+#pragma unroll
+    for (int u = 0; u < GPW; ++u) {
+        float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+        for (int q = 0; q < kWordsPerSub; ++q) {
+            const int wi = u * kWordsPerSub + q;
+            const uint32_t word = words[wi];
+            const uint32_t e0 = lds_u32(byte_into_base<0>(word, rt[2 * wi]));
+            const uint32_t e1 = lds_u32_hi(byte_into_base<1>(word, rt[2 * wi]));
+            const uint32_t e2 = lds_u32(byte_into_base<2>(word, rt[2 * wi + 1]));
+            const uint32_t e3 = lds_u32_hi(byte_into_base<3>(word, rt[2 * wi + 1]));
+            const float2 f0 = __half22float2(*(const __half2 *)&e0), f1 = __half22float2(*(const __half2 *)&e1);
+            const float2 f2 = __half22float2(*(const __half2 *)&e2), f3 = __half22float2(*(const __half2 *)&e3);
+            a0 += f0.x; b0 += f0.y;
+            a1 += f1.x; b1 += f1.y;
+            a0 += f2.x; b0 += f2.y;
+            a1 += f3.x; b1 += f3.y;
+        }
+        s0[u] = a0 + a1;
+        s1[u] = b0 + b1;
+    }
+}
+
+// One duo for two rows of x: four totals (row, oct) per lane; after the exchange lane j of a
+// row's four lanes holds the total of (x row j >> 1, oct j & 1) and adds it to that
+// accumulator.  `prow` as in compute_tile; `row_stride` = accumulator elements per row of x.
+template <int Q, int GPW>
+__device__ __forceinline__ void compute_tile2(const Tile<Q, GPW> &t, const uint32_t (&rt)[8],
+                                              const float (&xsu0)[GPW], const float (&xsu1)[GPW], float *prow,
+                                              int row_stride, int lane) {
+    float v[2][2];   // [x row][oct]
+#pragma unroll
+    for (int ou = 0; ou < 2; ++ou) {
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int u = 0; u < GPW; ++u) {
+            const float z = meta_value<GPW>(t.mt[Q], ou * GPW + u);
+            t0 += z * xsu0[u];
+            t1 += z * xsu1[u];
+        }
+#pragma unroll
+        for (int p = 0; p < Q; ++p) {
+            float s0[GPW], s1[GPW];
+            lookup_word2<GPW>(t.w[ou][p], rt, s0, s1);
+#pragma unroll
+            for (int u = 0; u < GPW; ++u) {
+                const float al = meta_value<GPW>(t.mt[p], ou * GPW + u);
+                t0 += al * s0[u];
+                t1 += al * s1[u];
+            }
+        }
+        v[0][ou] = t0;
+        v[1][ou] = t1;
+    }
+    const int j = lane & 3;
+    const bool odd = j & 1, hi = j & 2;
+    float k0 = odd ? v[0][1] : v[0][0], k1 = odd ? v[1][1] : v[1][0];       // this lane's oct, both rows
+    k0 += __shfl_xor_sync(0xffffffffu, odd ? v[0][0] : v[0][1], 1);
+    k1 += __shfl_xor_sync(0xffffffffu, odd ? v[1][0] : v[1][1], 1);
+    float keep = hi ? k1 : k0;
+    keep += __shfl_xor_sync(0xffffffffu, hi ? k0 : k1, 2);
+    atomicAdd(prow + (hi ? row_stride : 0) + (odd ? kOctRows : 0), keep);
+}
+
 // One duo: both octs' totals, the 4-lane reduction, and the add into the row's fp32
 // accumulator (a reduction without return value: the slices of a row come from different
 // CTAs).  `prow` points at acc[row of (first oct, this lane's r)].
@@ -429,7 +518,7 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     sg.counters = jb.counters + (long long)w.mrow * jb.blocks;
     sg.y = jb.y;
     sg.y_base = (long long)w.mrow * jb.n;
-    sg.n = jb.n; sg.np = jb.np; sg.slices = jb.slices;
+    sg.n = jb.n; sg.np = jb.np; sg.slices = jb.slices; sg.k = jb.k;
     sg.duo_a = da; sg.duo_b = db;
     sg.x_dtype = jb.x_dtype; sg.y_dtype = jb.y_dtype;
     sg.mrow = w.mrow; sg.blocks = jb.blocks;
@@ -439,11 +528,14 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     return (const uint16_t *)jb.x + (long long)w.mrow * jb.k + (long long)s * kSliceK;
 }
 
-template <int Q, int GPW>
+// R = rows of x one pass serves: 1, or 2 with half2 table entries {row, row + 1}.
+template <int Q, int GPW, int R>
 __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_constant__ GemvArgs a) {
+    static_assert(R == 1 || R == 2, "rows per pass");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int mrow = blockIdx.y;
+    const int mrow = a.row_base + blockIdx.y * R;
+    constexpr uint32_t kX = R == 2 ? kAuxX2 : kAuxX;          // activation slices: [slot][row][512]
 
     // The table block must start on a 64 KB boundary of the shared window.
     const uint32_t sbase = smem_u32(smem_raw);
@@ -454,7 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         return;
     }
     unsigned char *aux = smem_raw + (aux_u32 - sbase);
-    float *xsum = (float *)(aux + kAuxXsum);
+    float *xsum = (float *)(aux + (R == 2 ? kAuxXsum2 : kAuxXsum));    // [row][16]
     int *fail = (int *)(aux + kAuxFlag);
     Seg *ring = (Seg *)(aux + kAuxSeg);
     const uint32_t mb_desc = aux_u32 + kAuxMbarDesc, mb_x = aux_u32 + kAuxMbarX;
@@ -487,14 +579,16 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                     pdl_wait();
                     waited = true;
                 }
-                uint16_t *xs = (uint16_t *)(aux + kAuxX) + slot * kSliceK;
-                for (int i = valid + lane; i < kSliceK; i += 32) xs[i] = 0;
+                uint16_t *xs = (uint16_t *)(aux + kX) + slot * (R * kSliceK);
+                for (int rr = 0; rr < R; ++rr)
+                    for (int i = valid + lane; i < kSliceK; i += 32) xs[rr * kSliceK + i] = 0;
                 __syncwarp();
                 if (lane == 0) {
                     fence_proxy_async();
-                    mbar_expect_tx(mb_x + 8 * slot, (uint32_t)valid * 2u);
-                    tma_bulk_g2s(aux_u32 + kAuxX + slot * kSliceK * 2, src, (uint32_t)valid * 2u,
-                                 mb_x + 8 * slot);
+                    mbar_expect_tx(mb_x + 8 * slot, (uint32_t)valid * 2u * R);
+                    for (int rr = 0; rr < R; ++rr)
+                        tma_bulk_g2s(aux_u32 + kX + (slot * R + rr) * kSliceK * 2, src + (long long)rr * sg.k,
+                                     (uint32_t)valid * 2u, mb_x + 8 * slot);
                 }
             }
         };
@@ -562,7 +656,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                 if (mask) __threadfence();
                 // lane = row of a finished block; several blocks per round trip
                 while (mask) {
-                    float v[8];
+                    float v[8], v2[R == 2 ? 8 : 1];
                     int rows[8];
                     unsigned mm = mask;
 #pragma unroll
@@ -573,6 +667,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                             mm &= mm - 1;
                             rows[b] = __shfl_sync(0xffffffffu, blk, src_lane) * kBlockRows + lane;
                             v[b] = ldcg_f32(sg.acc + rows[b]);
+                            if constexpr (R == 2) v2[b] = ldcg_f32(sg.acc + sg.np + rows[b]);
                         }
                     }
 #pragma unroll
@@ -581,6 +676,12 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                             sg.acc[rows[b]] = 0.f;
                             float o = v[b];
                             if (sg.bias && rows[b] < sg.n) o += __half2float(__ushort_as_half(sg.bias[rows[b]]));
+                            if constexpr (R == 2) {       // the second row of x of this pass
+                                sg.acc[sg.np + rows[b]] = 0.f;
+                                float o2 = v2[b];
+                                if (sg.bias && rows[b] < sg.n) o2 += __half2float(__ushort_as_half(sg.bias[rows[b]]));
+                                if (rows[b] < sg.n) store_y(sg.y, sg.y_base + sg.n + rows[b], o2, sg.y_dtype);
+                            }
                             if (!tp) {
                                 if (rows[b] < sg.n) store_y(sg.y, sg.y_base + rows[b], o, sg.y_dtype);
                             } else {
@@ -649,12 +750,13 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
     const uint8_t *pl;
     const uint16_t *mp;
     float *prow;
-    int d, dend, x_dtype;
+    int d, dend, x_dtype, acc_stride = 0;
 
     auto open_segment = [&](const Seg &sg) {
         d = sg.duo_a + warp;
         dend = sg.duo_b;
         x_dtype = sg.x_dtype;
+        acc_stride = sg.np;
         pl = sg.planes + (long long)warp * kDuoPlaneBytes + lane * 16;
         mp = sg.meta + (long long)warp * kDuoMetaElems + lane * (2 * GPW);
         prow = sg.acc + (long long)d * 16 + r;
@@ -674,48 +776,71 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         named_bar_sync<kBarConsumers, kConsumers>();     // everyone is done with the old table
         if (!mbar_wait_bounded(mb_x + 8 * slot, (i >> 1) & 1)) *fail = 1;
         if (i == 0) pdl_wait();   // satisfied by now; orders this thread's writes after the previous grid
-        const uint16_t *xs = (const uint16_t *)(aux + kAuxX) + slot * kSliceK;
-        // group sums (warp 0) and the 64 tables of 256 subset sums (all consumer warps)
-        if (warp == 0) {
+        const uint16_t *xs = (const uint16_t *)(aux + kX) + slot * (R * kSliceK);
+        // group sums (warps 0..R-1) and the 64 tables of 256 subset sums (all consumer warps)
+        if (warp < R) {
             float part = 0.f;
 #pragma unroll
-            for (int q2 = 0; q2 < 16; ++q2) part += x_to_float(xs[lane * 16 + q2], x_dtype);
+            for (int q2 = 0; q2 < 16; ++q2) part += x_to_float(xs[warp * kSliceK + lane * 16 + q2], x_dtype);
             constexpr int lanes_per_group = 8 >> (3 - gshift);   // g / 16 lanes: 8, 4 or 2
 #pragma unroll
             for (int dd = 1; dd < lanes_per_group; dd <<= 1) part += __shfl_xor_sync(0xffffffffu, part, dd);
-            if ((lane & (lanes_per_group - 1)) == 0) xsum[lane / lanes_per_group] = part;
+            if ((lane & (lanes_per_group - 1)) == 0) xsum[warp * 16 + lane / lanes_per_group] = part;
         }
         {
             const int h = warp & 1, ehi = warp >> 1;   // bank-row, top three index bits
             const int c = 16 * (lane >> 3) + 2 * (lane & 7) + h;
-            const uint4 raw = *(const uint4 *)(xs + 8 * c);
-            const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-            float xv[8];
-#pragma unroll
-            for (int q2 = 0; q2 < 4; ++q2) {
-                xv[2 * q2] = x_to_float((uint16_t)(rw[q2] & 0xffffu), x_dtype);
-                xv[2 * q2 + 1] = x_to_float((uint16_t)(rw[q2] >> 16), x_dtype);
-            }
-            float base = 0.f;
-            if (ehi & 1) base += xv[5];
-            if (ehi & 2) base += xv[6];
-            if (ehi & 4) base += xv[7];
-            float tv[32];
-            tv[0] = base;
-#pragma unroll
-            for (int b = 0; b < 5; ++b)
-#pragma unroll
-                for (int e = 0; e < (1 << b); ++e) tv[(1 << b) + e] = tv[e] + xv[b];
             const uint32_t dst = tbl + (uint32_t)ehi * (32u * 256u) + 4u * lane + 128u * h;
+            uint32_t packed[R == 2 ? 32 : 1];    // two-row passes: row 0's entries as fp16 bits
 #pragma unroll
-            for (int e = 0; e < 32; ++e) sts_f32(dst + (uint32_t)e * 256u, tv[e]);
+            for (int rr = 0; rr < R; ++rr) {
+                const uint4 raw = *(const uint4 *)(xs + rr * kSliceK + 8 * c);
+                const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+                float xv[8];
+#pragma unroll
+                for (int q2 = 0; q2 < 4; ++q2) {
+                    xv[2 * q2] = x_to_float((uint16_t)(rw[q2] & 0xffffu), x_dtype);
+                    xv[2 * q2 + 1] = x_to_float((uint16_t)(rw[q2] >> 16), x_dtype);
+                }
+                float base = 0.f;
+                if (ehi & 1) base += xv[5];
+                if (ehi & 2) base += xv[6];
+                if (ehi & 4) base += xv[7];
+                float tv[32];
+                tv[0] = base;
+#pragma unroll
+                for (int b = 0; b < 5; ++b)
+#pragma unroll
+                    for (int e = 0; e < (1 << b); ++e) tv[(1 << b) + e] = tv[e] + xv[b];
+                if constexpr (R == 1) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) sts_f32(dst + (uint32_t)e * 256u, tv[e]);
+                } else if (rr == 0) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) packed[e] = __half_as_ushort(__float2half_rn(tv[e]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        sts_u32(dst + (uint32_t)e * 256u,
+                                packed[e] | ((uint32_t)__half_as_ushort(__float2half_rn(tv[e])) << 16));
+                }
+            }
         }
         named_bar_sync<kBarConsumers, kConsumers>();
         asm volatile("" ::: "memory");
 
-        float xsu[GPW];
+        float xsu[GPW], xsu1[GPW];
 #pragma unroll
-        for (int uu = 0; uu < GPW; ++uu) xsu[uu] = xsum[GPW * j + (uu ^ (r >> gshift))];
+        for (int uu = 0; uu < GPW; ++uu) {
+            xsu[uu] = xsum[GPW * j + (uu ^ (r >> gshift))];
+            xsu1[uu] = R == 2 ? xsum[16 + GPW * j + (uu ^ (r >> gshift))] : 0.f;
+        }
+        auto compute = [&](const Tile<Q, GPW> &t, float *row) {
+            if constexpr (R == 2)
+                compute_tile2<Q, GPW>(t, rt, xsu, xsu1, row, acc_stride, lane);
+            else
+                compute_tile<Q, GPW>(t, rt, xsu, row, lane);
+        };
 
         // stream: ring of three register tiles, two loads in flight behind the one in use
         constexpr long long kStepP = kConsumerWarps * kDuoPlaneBytes;
@@ -724,15 +849,15 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         if (kRing == 3) {
             while (d < dend) {
                 if (d + 2 * kConsumerWarps < dend) load_tile<Q, GPW>(t2, pl + 2 * kStepP, mp + 2 * kStepM);
-                compute_tile<Q, GPW>(t0, rt, xsu, prow, lane);
+                compute(t0, prow);
                 d += kConsumerWarps;
                 if (d >= dend) break;
                 if (d + 2 * kConsumerWarps < dend) load_tile<Q, GPW>(t0, pl + 3 * kStepP, mp + 3 * kStepM);
-                compute_tile<Q, GPW>(t1, rt, xsu, prow + kStepRow, lane);
+                compute(t1, prow + kStepRow);
                 d += kConsumerWarps;
                 if (d >= dend) break;
                 if (d + 2 * kConsumerWarps < dend) load_tile<Q, GPW>(t1, pl + 4 * kStepP, mp + 4 * kStepM);
-                compute_tile<Q, GPW>(t2, rt, xsu, prow + 2 * kStepRow, lane);
+                compute(t2, prow + 2 * kStepRow);
                 d += kConsumerWarps;
                 pl += 3 * kStepP;
                 mp += 3 * kStepM;
@@ -741,11 +866,11 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         } else {
             while (d < dend) {
                 if (d + kConsumerWarps < dend) load_tile<Q, GPW>(t1, pl + kStepP, mp + kStepM);
-                compute_tile<Q, GPW>(t0, rt, xsu, prow, lane);
+                compute(t0, prow);
                 d += kConsumerWarps;
                 if (d >= dend) break;
                 if (d + kConsumerWarps < dend) load_tile<Q, GPW>(t0, pl + 2 * kStepP, mp + 2 * kStepM);
-                compute_tile<Q, GPW>(t1, rt, xsu, prow + kStepRow, lane);
+                compute(t1, prow + kStepRow);
                 d += kConsumerWarps;
                 pl += 2 * kStepP;
                 mp += 2 * kStepM;
@@ -991,12 +1116,12 @@ static int launch_pdl(KernelT kernel, dim3 grid, dim3 block, size_t smem, cudaSt
 // wherever the window starts: 64 KB of slack, the table, the aux area.
 constexpr uint32_t kLut8DynSmem = 65536 - 1024 + kTableBytes + kAuxBytes;
 
-template <int Q, int GPW>
+template <int Q, int GPW, int R>
 static int launch_lut8_inst(const GemvArgs &args, dim3 grid, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     HLQ_CUDA(cudaGetDevice(&dev));
-    auto kernel = lut8_gemv_kernel<Q, GPW>;
+    auto kernel = lut8_gemv_kernel<Q, GPW, R>;
     if (!configured[dev & 63]) {
         HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)kLut8DynSmem));
@@ -1005,9 +1130,10 @@ static int launch_lut8_inst(const GemvArgs &args, dim3 grid, cudaStream_t stream
     return launch_pdl(kernel, grid, dim3(kThreads), kLut8DynSmem, stream, args);
 }
 
-static int launch_lut8_any(int q, int gpw, const GemvArgs &a, dim3 grid, cudaStream_t stream) {
+template <int R>
+static int launch_lut8_rows(int q, int gpw, const GemvArgs &a, dim3 grid, cudaStream_t stream) {
 #define HLQ_CASE(QV, GV) \
-    if (q == QV && gpw == GV) return launch_lut8_inst<QV, GV>(a, grid, stream);
+    if (q == QV && gpw == GV) return launch_lut8_inst<QV, GV, R>(a, grid, stream);
     HLQ_CASE(1, 1) HLQ_CASE(1, 2) HLQ_CASE(1, 4)
     HLQ_CASE(2, 1) HLQ_CASE(2, 2) HLQ_CASE(2, 4)
     HLQ_CASE(3, 1) HLQ_CASE(3, 2) HLQ_CASE(3, 4)
@@ -1019,6 +1145,23 @@ static int launch_lut8_any(int q, int gpw, const GemvArgs &a, dim3 grid, cudaStr
 static int env_int(const char *name, int dflt) {
     const char *v = getenv(name);
     return v && *v ? atoi(v) : dflt;
+}
+
+// grid.y = rows of x.  Two or more rows go through passes of two rows each (half2 table
+// entries: one lookup serves both) plus a single-row pass for an odd last row.  The table
+// entries of such a pass are rounded to fp16 (2^-11, as the reference's tables are), which is
+// below the rounding of a 16-bit output; fp32 outputs therefore keep one row per pass and
+// fp32 entries, and so do the fused all-reduce and HLQ_GEMV_PAIR_ROWS=0.
+static int launch_lut8_any(int q, int gpw, const GemvArgs &a_in, dim3 grid, cudaStream_t stream) {
+    static const int pair_rows = env_int("HLQ_GEMV_PAIR_ROWS", 1);
+    const int m = (int)grid.y;
+    GemvArgs a = a_in;
+    a.row_base = 0;
+    if (m < 2 || a.tp || a.y_is_f32 || !pair_rows) return launch_lut8_rows<1>(q, gpw, a, grid, stream);
+    int rc = launch_lut8_rows<2>(q, gpw, a, dim3(grid.x, m / 2), stream);
+    if (rc || !(m & 1)) return rc;
+    a.row_base = m - 1;
+    return launch_lut8_rows<1>(q, gpw, a, dim3(grid.x, 1), stream);
 }
 
 static void fill_job(Job &j, const hlq_weight *w, const StreamDims &d, const void *x, int x_dtype,
@@ -1058,6 +1201,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         a.total_units = launch_units(d.slices, d.duos, 0);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
+        a.y_is_f32 = y_dtype == HLQ_F32;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         int ctas = force_ctas > 0 ? force_ctas : di->sms;
@@ -1125,6 +1269,7 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         a.total_units = launch_units(d.slices, d.duos, 0);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
+        a.y_is_f32 = y_dtype == HLQ_F32;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         int ctas = di->sms;
@@ -1410,6 +1555,7 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.seg_cost = g->seg_cost;
     a.status = (int *)g->d_scratch;
     a.dyn_smem = kLut8DynSmem;
+    a.y_is_f32 = g->jobs_host[0].y_dtype == HLQ_F32;
     int ctas = force_ctas > 0 ? force_ctas : di->sms;
     if (g->duo_units < ctas) ctas = (int)g->duo_units;
     return launch_lut8_any(g->q, g->gpw, a, dim3(ctas, m), (cudaStream_t)stream);
