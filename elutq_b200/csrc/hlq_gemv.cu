@@ -358,12 +358,13 @@ __device__ __forceinline__ void lookup_word2(const uint4 &w, const uint32_t (&rt
             const uint32_t e1 = lds_u32_hi(byte_into_base<1>(word, rt[2 * wi]));
             const uint32_t e2 = lds_u32(byte_into_base<2>(word, rt[2 * wi + 1]));
             const uint32_t e3 = lds_u32_hi(byte_into_base<3>(word, rt[2 * wi + 1]));
-            const float2 f0 = __half22float2(*(const __half2 *)&e0), f1 = __half22float2(*(const __half2 *)&e1);
-            const float2 f2 = __half22float2(*(const __half2 *)&e2), f3 = __half22float2(*(const __half2 *)&e3);
+            // two entries are added as half2 (one more fp16 rounding), then widened: the sums
+            // of 16 activations still sit far inside the fp16 range for any input the
+            // reference's fp16 accumulation over whole groups can handle
+            const float2 f0 = __half22float2(__hadd2(*(const __half2 *)&e0, *(const __half2 *)&e2));
+            const float2 f1 = __half22float2(__hadd2(*(const __half2 *)&e1, *(const __half2 *)&e3));
             a0 += f0.x; b0 += f0.y;
             a1 += f1.x; b1 += f1.y;
-            a0 += f2.x; b0 += f2.y;
-            a1 += f3.x; b1 += f3.y;
         }
         s0[u] = a0 + a1;
         s1[u] = b0 + b1;
