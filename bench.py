@@ -452,7 +452,7 @@ def run_decode(args):
                        "glue": ("PyTorch ops (norm, rope, attention, silu, lm_head) inside one CUDA graph"
                                 if args.torch_glue else
                                 "own kernels (residual+RMSNorm, RoPE+KV append+attention, gated SiLU, argmax), "
-                                "cuBLAS fp16 lm_head, one CUDA graph"),
+                                "w4g128 HLQ lm_head, one CUDA graph"),
                        "collectives": ("all-reduce fused into the o and down GEMV kernels (peer stores over NVLink)"
                                        if args.fused_allreduce else "NCCL all-reduce after o and down")
                                       + ", NCCL all-gather of the arg-max"},

@@ -4,7 +4,8 @@ node.  It is the caller of the hot path that the reference's `llama::forward` is
 single-token attention, o, RMSNorm, gate/up, SiLU*up, down; then the final norm, lm_head and
 argmax.  The quantized linears and the glue between them (`glue.py`: residual + RMSNorm,
 RoPE + KV append + attention as one kernel, gated SiLU, argmax) are this package's kernels;
-the embedding row copy and the fp16 lm_head product are library calls.  `fused_glue=False`
+the embedding row copy is a library call; lm_head is a w4g128 HLQ linear as in the reference
+(HLQ.py:76-78), or with `quantized_lm_head=False` an fp16 library product.  `fused_glue=False`
 runs the same glue as PyTorch ops instead (the parity reference of the tests).  The whole
 step is replayed as one CUDA graph; the position lives in device memory.
 
@@ -59,7 +60,7 @@ class TPDecoder:
 
     def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
                  group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False,
-                 fused_glue: bool = True):
+                 fused_glue: bool = True, quantized_lm_head: bool = True):
         if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
         self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
@@ -71,9 +72,9 @@ class TPDecoder:
         self.layers = []
         self.linear_bytes = 0
 
-        def load(n, k, mode, lseed):
+        def load(n, k, mode, lseed, bits=c.bits, groupsize=c.groupsize):
             gen.manual_seed(lseed)          # every rank draws the full tensor and keeps its shard
-            lin = _random_export(n, k, c.bits, c.groupsize, gen, device)
+            lin = _random_export(n, k, bits, groupsize, gen, device)
             w = HLQWeight.from_export(lin, device=device.index, tp_rank=rank, tp_size=world, shard_mode=mode)
             self.linear_bytes += w.info.algorithmic_bytes
             return w
@@ -119,13 +120,20 @@ class TPDecoder:
         self.embed = (torch.randn((c.vocab, c.hidden), device=device, generator=gen) * 0.5).to(dt)
         self.norm = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
         vs = c.vocab // world
-        self.lm_head = torch.empty((vs, c.hidden), dtype=dt, device=device)
-        for r0 in range(0, c.vocab, 8192):      # every rank draws all rows, keeps its slice
-            blk = (torch.randn((min(8192, c.vocab - r0), c.hidden), device=device, generator=gen) * 0.02).to(dt)
-            lo, hi = max(r0, rank * vs), min(r0 + blk.shape[0], (rank + 1) * vs)
-            if lo < hi:
-                self.lm_head[lo - rank * vs:hi - rank * vs] = blk[lo - r0:hi - r0]
-        n_max = max(c.hidden, c.ffn // world, q_dim // world)     # scratch grows with the output rows
+        self.lm_head = self.lm_w = None
+        if quantized_lm_head:
+            # the reference quantizes lm_head to w4g128 whatever the body uses (HLQ.py:76-78)
+            self.lm_w = load(c.vocab, c.hidden, rows, seed + 100007, bits=4, groupsize=128)
+            self.logits = torch.empty((1, vs), dtype=dt, device=device)
+        else:
+            self.lm_head = torch.empty((vs, c.hidden), dtype=dt, device=device)
+            for r0 in range(0, c.vocab, 8192):      # every rank draws all rows, keeps its slice
+                blk = (torch.randn((min(8192, c.vocab - r0), c.hidden), device=device, generator=gen) * 0.02).to(dt)
+                lo, hi = max(r0, rank * vs), min(r0 + blk.shape[0], (rank + 1) * vs)
+                if lo < hi:
+                    self.lm_head[lo - rank * vs:hi - rank * vs] = blk[lo - r0:hi - r0]
+        # scratch grows with the output rows
+        n_max = max(c.hidden, c.ffn // world, q_dim // world, vs if quantized_lm_head else 0)
         need = workspace_bytes(1, c.hidden, n_max, c.bits, c.groupsize)
         self.ws = Workspace(need, device)
         pos = c.ctx - 1
@@ -158,6 +166,12 @@ class TPDecoder:
                                            out.data_ptr(), _lib.HLQ_F16, self.ws.ptr, self.ws.nbytes, w.handle,
                                            torch.cuda.current_stream(self.dev).cuda_stream)
         _lib.check(st, "hlq_linear_forward")
+
+    def _logits(self, xn):
+        if self.lm_w is None:
+            return torch.matmul(xn, self.lm_head.t())
+        self._linear(self.lm_w, xn, self.logits)
+        return self.logits
 
     def _rope(self, t, heads):
         """Pairs (j, j + dhead/2) as in the reference (arm_rotary.cpp:28-49); fp32 math."""
@@ -220,7 +234,7 @@ class TPDecoder:
             delta = L["d_o"]
         xn = self.layers[0]["xn"]
         glue.rmsnorm(delta, self.norm, 1e-5, out=xn, residual=x, res_out=x)
-        logits = torch.matmul(xn, self.lm_head.t())                  # this rank's slice of the vocabulary (fp16)
+        logits = self._logits(xn)                                     # this rank's slice of the vocabulary (fp16)
         glue.argmax(logits.view(-1), self.next_index, self.next_value)
         self.last_logits = logits
         return self._pick(self.next_value, self.next_index)
@@ -271,7 +285,7 @@ class TPDecoder:
             self._row_parallel(L["down"], L["act"], L["d_o"])
             x.add_(L["d_o"])
         xn = norm(x, self.norm)
-        logits = torch.matmul(xn, self.lm_head.t())
+        logits = self._logits(xn)
         val, idx = logits.float().max(dim=1)
         self.last_logits = logits
         return self._pick(val, idx.int())
@@ -296,7 +310,7 @@ class TPDecoder:
         per_layer = (2 if self.grouped else 5) + 2          # qkv, gate/up (+ o, down below)
         if self.fused_glue:
             per_layer += 4                                  # two norms, attention, gated silu
-        return len(self.layers) * per_layer + (2 if self.fused_glue else 0)
+        return len(self.layers) * per_layer + (2 if self.fused_glue else 0) + (1 if self.lm_w is not None else 0)
 
     def hidden_after_step(self):
         return self.x
