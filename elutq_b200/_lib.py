@@ -79,6 +79,11 @@ SIGNATURES = {
     "hlq_group_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
     "hlq_group_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int64), POINTER(c_int64)]),
     "hlq_group_free": (c_int, [c_void_p]),
+    "hlq_linear_forward_op": (c_int, [c_int] * 3 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t, c_void_p,
+                                                    c_void_p, c_void_p]),
+    "hlq_linear_forward_allreduce_op": (c_int, [c_int] * 3 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t,
+                                                c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hlq_group_bind_op": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),
     "hlq_rmsnorm": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "hlq_gated_silu": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "hlq_argmax": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
@@ -90,6 +95,14 @@ SIGNATURES = {
     "hlq_kernel_launch_count": (c_int64, []),
     "hlq_abi_version": (c_int, []),
 }
+
+class InputOp(ctypes.Structure):
+    """hlq_input_op: a transform of the activations fused into the LUT GEMV's table build."""
+    _fields_ = [("kind", c_int), ("eps", c_float), ("d_second", c_void_p), ("d_gamma", c_void_p),
+                ("d_res_out", c_void_p)]
+
+
+HLQ_INPUT_PLAIN, HLQ_INPUT_GATED_SILU, HLQ_INPUT_ADD_RMSNORM = 0, 1, 2
 
 _LIB = None
 

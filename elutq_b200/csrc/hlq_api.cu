@@ -335,6 +335,22 @@ int hlq_workspace_status(const void *d_workspace, void *stream, int *kernel_stat
     return *kernel_status ? HLQ_ERR_KERNEL : HLQ_OK;
 }
 
+int hlq_linear_forward_op(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,
+                          void *d_workspace, size_t workspace_bytes, const hlq_weight *w, const hlq_input_op *op,
+                          void *stream_) {
+    if (!w || m < 0) return HLQ_ERR_INVALID_ARGUMENT;
+    if (k != w->k || n != w->n) return HLQ_ERR_SHAPE;
+    if (m == 0) return HLQ_OK;
+    if (!d_x || !d_y) return HLQ_ERR_INVALID_ARGUMENT;
+    if (m > hlq::kLutMaxM) return HLQ_ERR_UNSUPPORTED;
+    if (y_dtype != HLQ_F16 && y_dtype != HLQ_BF16 && y_dtype != HLQ_F32) return HLQ_ERR_UNSUPPORTED;
+    int cur = -1;
+    HLQ_CUDA(cudaGetDevice(&cur));
+    if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;
+    return hlq::launch_lut8_gemv(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes,
+                                 (cudaStream_t)stream_, op);
+}
+
 int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int x_dtype, void *d_y,
                             int y_dtype, void *d_workspace, size_t workspace_bytes, const hlq_weight *w,
                             void *stream_) {

@@ -41,6 +41,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#ifdef HLQ_GEMV_PROF
+#include <cstdio>
+#endif
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -76,6 +79,15 @@ struct Job {
     int n, k, np, slices, duos, blocks;
     int x_dtype, y_dtype;
     long long unit_begin; // first (slice, duo) unit of this job in the launch
+    // Optional transform of the input while the tables are built (one row of x per pass):
+    //   HLQ_INPUT_GATED_SILU:  x_eff = fp16(x2 * x / (1 + exp(-x)))
+    //   HLQ_INPUT_ADD_RMSNORM: t = x + x2 (x2 may be null), res_out = fp16(t) (may be null),
+    //                          x_eff = fp16(fp16(t) * gamma / sqrt(mean(t^2) + eps))
+    int xop;
+    float eps;
+    const void *x2;          // [m][k] fp16
+    const uint16_t *gamma;   // [k] fp16
+    uint16_t *res_out;       // [m][k] fp16, distinct from x and x2
 };
 
 // Peer-mapped buffers of a fused all-reduce (one per tensor-parallel communicator), in device
@@ -98,6 +110,7 @@ struct GemvArgs {
     int seg_cost;         // units charged per (job, slice) when the work is split over the CTAs
     int row_base;         // first row of x this launch serves (grid.y passes of R rows follow)
     int y_is_f32;         // host only: fp32 outputs keep one row per pass (fp32 table entries)
+    int one_row_passes;   // host only: a job has an input transform (one row of x per pass)
     Job single;
 };
 
@@ -115,6 +128,8 @@ struct Seg {
     int x_dtype, y_dtype;
     int mrow, blocks;
     int live;
+    int slice;              // slice index of the segment
+    const Job *jb;          // the job (for its input transform)
 };
 
 // aux region layout (bytes from its start)
@@ -123,12 +138,17 @@ constexpr uint32_t kAuxXsum = 2048;    // up to 16 group sums (fp32)
 constexpr uint32_t kAuxMbarDesc = 2112;  // 2 mbarriers
 constexpr uint32_t kAuxMbarX = 2128;     // 2 mbarriers
 constexpr uint32_t kAuxFlag = 2144;    // int: CTA-wide failure flag
-constexpr uint32_t kAuxSeg = 2304;     // 2 x Seg (<= 128 bytes each)
+constexpr uint32_t kAuxRed = 2944;     // 16 partial sums of an RMS over a row of x
+constexpr uint32_t kAuxSeg = 3072;     // 2 x Seg (<= 192 bytes each)
+constexpr uint32_t kAuxSegSlot = 192;
+constexpr uint32_t kAuxX2 = 4096;      // two-row passes: 2 slots x 2 rows x 512 activations; one-row
+                                       // passes with an input transform: 2 slots x 512 of the second input
+constexpr uint32_t kAuxGamma = 6144;   // input transform: 2 slots x 512 RMSNorm weights
 constexpr uint32_t kAuxTp = 2560;      // copy of the TpDev of a fused all-reduce (<= 256 bytes)
 constexpr uint32_t kAuxXsum2 = 2816;   // two-row passes: 2 x 16 group sums
-constexpr uint32_t kAuxX2 = 4096;      // two-row passes: 2 slots x 2 rows x 512 activations
 static_assert(sizeof(TpDev) <= 256, "TpDev must fit its slot");
-static_assert(sizeof(Seg) <= 128, "Seg must fit its slot");
+static_assert(sizeof(Seg) <= kAuxSegSlot, "Seg must fit its slot");
+static_assert(kAuxGamma + 2048 <= kAuxBytes, "aux area");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -524,15 +544,20 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     sg.x_dtype = jb.x_dtype; sg.y_dtype = jb.y_dtype;
     sg.mrow = w.mrow; sg.blocks = jb.blocks;
     sg.live = 1;
+    sg.slice = s;
+    sg.jb = w.a->njobs == 0 ? &w.a->single : &w.a->jobs[w.jidx];
     valid = min(kSliceK, jb.k - s * kSliceK);
     w.u += db - da;
     return (const uint16_t *)jb.x + (long long)w.mrow * jb.k + (long long)s * kSliceK;
 }
 
 // R = rows of x one pass serves: 1, or 2 with half2 table entries {row, row + 1}.
-template <int Q, int GPW, int R>
+// XOP: the instantiation that applies the jobs' input transforms (one-row passes only), kept
+// apart so that the plain kernel does not carry its registers.
+template <int Q, int GPW, int R, bool XOP>
 __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_constant__ GemvArgs a) {
     static_assert(R == 1 || R == 2, "rows per pass");
+    static_assert(!XOP || R == 1, "input transforms run in one-row passes");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int mrow = a.row_base + blockIdx.y * R;
@@ -552,6 +577,14 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
     Seg *ring = (Seg *)(aux + kAuxSeg);
     const uint32_t mb_desc = aux_u32 + kAuxMbarDesc, mb_x = aux_u32 + kAuxMbarX;
 
+#ifdef HLQ_GEMV_PROF
+    unsigned long long gt_entry;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_entry));
+#define GT_MARK(tag) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+        if (blockIdx.x == 0 || blockIdx.x == 100) printf("gt b%d %s abs %llu rel +%llu\n", blockIdx.x, tag, t_ % 1000000000ull, t_ - gt_entry); }
+#else
+#define GT_MARK(tag)
+#endif
     pdl_launch_dependents();
     if (tid == 0) {
         mbar_init(mb_desc, 1);
@@ -584,12 +617,29 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                 for (int rr = 0; rr < R; ++rr)
                     for (int i = valid + lane; i < kSliceK; i += 32) xs[rr * kSliceK + i] = 0;
                 __syncwarp();
+                // input transform (one-row passes): the slice of the second input and of gamma
+                const Job *jb = sg.jb;
+                const int xop = XOP ? jb->xop : 0;
+                const uint16_t *src2 = nullptr, *srcg = nullptr;
+                if (xop) {
+                    uint16_t *xs2 = (uint16_t *)(aux + kAuxX2) + slot * kSliceK;
+                    uint16_t *gs = (uint16_t *)(aux + kAuxGamma) + slot * kSliceK;
+                    const long long off = (long long)sg.mrow * sg.k + (long long)sg.slice * kSliceK;
+                    if (jb->x2) src2 = (const uint16_t *)jb->x2 + off;
+                    if (xop == HLQ_INPUT_ADD_RMSNORM) srcg = jb->gamma + (long long)sg.slice * kSliceK;
+                    for (int i = (src2 ? valid : 0) + lane; i < kSliceK; i += 32) xs2[i] = 0;
+                    for (int i = (srcg ? valid : 0) + lane; i < kSliceK; i += 32) gs[i] = 0;
+                }
+                __syncwarp();
                 if (lane == 0) {
                     fence_proxy_async();
-                    mbar_expect_tx(mb_x + 8 * slot, (uint32_t)valid * 2u * R);
+                    const uint32_t bytes = (uint32_t)valid * 2u;
+                    mbar_expect_tx(mb_x + 8 * slot, bytes * (R + (src2 ? 1 : 0) + (srcg ? 1 : 0)));
                     for (int rr = 0; rr < R; ++rr)
-                        tma_bulk_g2s(aux_u32 + kX + (slot * R + rr) * kSliceK * 2, src + (long long)rr * sg.k,
-                                     (uint32_t)valid * 2u, mb_x + 8 * slot);
+                        tma_bulk_g2s(aux_u32 + kX + (slot * R + rr) * kSliceK * 2, src + (long long)rr * sg.k, bytes,
+                                     mb_x + 8 * slot);
+                    if (src2) tma_bulk_g2s(aux_u32 + kAuxX2 + slot * kSliceK * 2, src2, bytes, mb_x + 8 * slot);
+                    if (srcg) tma_bulk_g2s(aux_u32 + kAuxGamma + slot * kSliceK * 2, srcg, bytes, mb_x + 8 * slot);
                 }
             }
         };
@@ -732,6 +782,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
             }
         }
         if (*fail && ftid == 0) atomicExch(a.status, 1);
+        if (ftid == 0) GT_MARK("fin_end");
         return;
     }
 
@@ -752,12 +803,24 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
     const uint16_t *mp;
     float *prow;
     int d, dend, x_dtype, acc_stride = 0;
+    // input transform of the current segment's job
+    const Job *cur_job = nullptr, *rms_job = nullptr;
+    int cur_slice = 0, cur_xop = 0, cur_k = 0;
+    bool cur_first = false;            // the segment starts its slice: it writes res_out
+    float inv_rms = 0.f;
 
     auto open_segment = [&](const Seg &sg) {
         d = sg.duo_a + warp;
         dend = sg.duo_b;
         x_dtype = sg.x_dtype;
         acc_stride = sg.np;
+        if (XOP) {
+            cur_job = sg.jb;
+            cur_slice = sg.slice;
+            cur_k = sg.k;
+            cur_first = sg.duo_a == 0;
+        }
+        cur_xop = XOP ? sg.jb->xop : 0;
         pl = sg.planes + (long long)warp * kDuoPlaneBytes + lane * 16;
         mp = sg.meta + (long long)warp * kDuoMetaElems + lane * (2 * GPW);
         prow = sg.acc + (long long)d * 16 + r;
@@ -775,14 +838,59 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
     for (int i = 0;; ++i) {
         const int slot = i & 1;
         named_bar_sync<kBarConsumers, kConsumers>();     // everyone is done with the old table
+        if (tid == 0 && i == 0) GT_MARK("desc_ok");
+        if (i == 0) pdl_wait();   // orders this thread's reads and writes after the previous grid
+        if (XOP && cur_xop == HLQ_INPUT_ADD_RMSNORM && cur_job != rms_job) {
+            // 1 / rms of the whole row t = x + x2, once per job and CTA (the rows sit in L2)
+            const uint4 *xr = (const uint4 *)((const uint16_t *)cur_job->x + (long long)mrow * cur_k);
+            const uint4 *x2r = cur_job->x2 ? (const uint4 *)((const uint16_t *)cur_job->x2 + (long long)mrow * cur_k)
+                                           : nullptr;
+            float ss = 0.f;
+            for (int v = tid; v < cur_k / 8; v += kConsumers) {
+                const uint4 av = xr[v];
+                uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+                if (x2r) bv = x2r[v];
+                const __half2 *ah = (const __half2 *)&av, *bh = (const __half2 *)&bv;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 fa = __half22float2(ah[e]), fb = __half22float2(bh[e]);
+                    const float t0 = fa.x + fb.x, t1 = fa.y + fb.y;
+                    ss += t0 * t0 + t1 * t1;
+                }
+            }
+#pragma unroll
+            for (int dd = 16; dd; dd >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, dd);
+            float *red = (float *)(aux + kAuxRed);
+            if (lane == 0) red[warp] = ss;
+            named_bar_sync<kBarConsumers, kConsumers>();
+            float tot = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < kConsumerWarps; ++w2) tot += red[w2];
+            inv_rms = 1.0f / sqrtf(tot / (float)cur_k + cur_job->eps);
+            rms_job = cur_job;
+            named_bar_sync<kBarConsumers, kConsumers>();     // red[] may be rewritten by the next job
+        }
         if (!mbar_wait_bounded(mb_x + 8 * slot, (i >> 1) & 1)) *fail = 1;
-        if (i == 0) pdl_wait();   // satisfied by now; orders this thread's writes after the previous grid
+        if (tid == 0 && i == 0) GT_MARK("x_ok");
         const uint16_t *xs = (const uint16_t *)(aux + kX) + slot * (R * kSliceK);
         // group sums (warps 0..R-1) and the 64 tables of 256 subset sums (all consumer warps)
+        const uint16_t *xs2 = (const uint16_t *)(aux + kAuxX2) + slot * kSliceK;     // input transform only
+        const uint16_t *gs = (const uint16_t *)(aux + kAuxGamma) + slot * kSliceK;
+        // transformed activation: the value the tables are built from (rounded to fp16 like
+        // the tensor the unfused kernels would have written)
+        auto x_eff = [&](float xv, int ch) {
+            if (!XOP || cur_xop == 0) return xv;
+            const float sv = __half2float(__ushort_as_half(xs2[ch]));
+            if (cur_xop == HLQ_INPUT_GATED_SILU)
+                return __half2float(__float2half_rn(sv * (xv / (1.0f + expf(-xv)))));
+            const float t16 = __half2float(__float2half_rn(xv + sv));
+            return __half2float(__float2half_rn(t16 * __half2float(__ushort_as_half(gs[ch])) * inv_rms));
+        };
         if (warp < R) {
             float part = 0.f;
 #pragma unroll
-            for (int q2 = 0; q2 < 16; ++q2) part += x_to_float(xs[warp * kSliceK + lane * 16 + q2], x_dtype);
+            for (int q2 = 0; q2 < 16; ++q2)
+                part += x_eff(x_to_float(xs[warp * kSliceK + lane * 16 + q2], x_dtype), lane * 16 + q2);
             constexpr int lanes_per_group = 8 >> (3 - gshift);   // g / 16 lanes: 8, 4 or 2
 #pragma unroll
             for (int dd = 1; dd < lanes_per_group; dd <<= 1) part += __shfl_xor_sync(0xffffffffu, part, dd);
@@ -802,6 +910,25 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                 for (int q2 = 0; q2 < 4; ++q2) {
                     xv[2 * q2] = x_to_float((uint16_t)(rw[q2] & 0xffffu), x_dtype);
                     xv[2 * q2 + 1] = x_to_float((uint16_t)(rw[q2] >> 16), x_dtype);
+                }
+                if (XOP && cur_xop) {
+                    if (cur_xop == HLQ_INPUT_ADD_RMSNORM && ehi == 0 && cur_first && cur_job->res_out &&
+                        cur_slice * kSliceK + 8 * c < cur_k) {
+                        // the residual stream's new value: written once per slice, by the
+                        // segment that starts it
+                        const uint4 sraw = *(const uint4 *)(xs2 + 8 * c);
+                        const __half2 *xh = (const __half2 *)&raw, *sh = (const __half2 *)&sraw;
+                        uint4 o;
+                        __half2 *oh = (__half2 *)&o;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 fa = __half22float2(xh[e]), fb = __half22float2(sh[e]);
+                            oh[e] = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+                        }
+                        *(uint4 *)(cur_job->res_out + (long long)mrow * cur_k + cur_slice * kSliceK + 8 * c) = o;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) xv[e] = x_eff(xv[e], 8 * c + e);
                 }
                 float base = 0.f;
                 if (ehi & 1) base += xv[5];
@@ -829,6 +956,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         }
         named_bar_sync<kBarConsumers, kConsumers>();
         asm volatile("" ::: "memory");
+        if (tid == 0 && i == 0) GT_MARK("table_ok");
 
         float xsu[GPW], xsu1[GPW];
 #pragma unroll
@@ -886,6 +1014,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         named_bar_arrive_dyn(kBarSegDone + slot, kThreads);
         if (!nx.live) break;
     }
+    if (tid == 0) GT_MARK("cons_end");
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1117,12 +1246,12 @@ static int launch_pdl(KernelT kernel, dim3 grid, dim3 block, size_t smem, cudaSt
 // wherever the window starts: 64 KB of slack, the table, the aux area.
 constexpr uint32_t kLut8DynSmem = 65536 - 1024 + kTableBytes + kAuxBytes;
 
-template <int Q, int GPW, int R>
+template <int Q, int GPW, int R, bool XOP>
 static int launch_lut8_inst(const GemvArgs &args, dim3 grid, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     HLQ_CUDA(cudaGetDevice(&dev));
-    auto kernel = lut8_gemv_kernel<Q, GPW, R>;
+    auto kernel = lut8_gemv_kernel<Q, GPW, R, XOP>;
     if (!configured[dev & 63]) {
         HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)kLut8DynSmem));
@@ -1131,10 +1260,10 @@ static int launch_lut8_inst(const GemvArgs &args, dim3 grid, cudaStream_t stream
     return launch_pdl(kernel, grid, dim3(kThreads), kLut8DynSmem, stream, args);
 }
 
-template <int R>
+template <int R, bool XOP>
 static int launch_lut8_rows(int q, int gpw, const GemvArgs &a, dim3 grid, cudaStream_t stream) {
 #define HLQ_CASE(QV, GV) \
-    if (q == QV && gpw == GV) return launch_lut8_inst<QV, GV, R>(a, grid, stream);
+    if (q == QV && gpw == GV) return launch_lut8_inst<QV, GV, R, XOP>(a, grid, stream);
     HLQ_CASE(1, 1) HLQ_CASE(1, 2) HLQ_CASE(1, 4)
     HLQ_CASE(2, 1) HLQ_CASE(2, 2) HLQ_CASE(2, 4)
     HLQ_CASE(3, 1) HLQ_CASE(3, 2) HLQ_CASE(3, 4)
@@ -1158,11 +1287,12 @@ static int launch_lut8_any(int q, int gpw, const GemvArgs &a_in, dim3 grid, cuda
     const int m = (int)grid.y;
     GemvArgs a = a_in;
     a.row_base = 0;
-    if (m < 2 || a.tp || a.y_is_f32 || !pair_rows) return launch_lut8_rows<1>(q, gpw, a, grid, stream);
-    int rc = launch_lut8_rows<2>(q, gpw, a, dim3(grid.x, m / 2), stream);
+    if (a.one_row_passes) return launch_lut8_rows<1, true>(q, gpw, a, grid, stream);
+    if (m < 2 || a.tp || a.y_is_f32 || !pair_rows) return launch_lut8_rows<1, false>(q, gpw, a, grid, stream);
+    int rc = launch_lut8_rows<2, false>(q, gpw, a, dim3(grid.x, m / 2), stream);
     if (rc || !(m & 1)) return rc;
     a.row_base = m - 1;
-    return launch_lut8_rows<1>(q, gpw, a, dim3(grid.x, 1), stream);
+    return launch_lut8_rows<1, false>(q, gpw, a, dim3(grid.x, 1), stream);
 }
 
 static void fill_job(Job &j, const hlq_weight *w, const StreamDims &d, const void *x, int x_dtype,
@@ -1177,10 +1307,39 @@ static void fill_job(Job &j, const hlq_weight *w, const StreamDims &d, const voi
     j.n = w->n; j.k = w->k; j.np = d.np; j.slices = d.slices; j.duos = d.duos; j.blocks = d.blocks;
     j.x_dtype = x_dtype; j.y_dtype = y_dtype;
     j.unit_begin = unit_begin;
+    j.xop = HLQ_INPUT_PLAIN;
+    j.eps = 0.f;
+    j.x2 = nullptr;
+    j.gamma = nullptr;
+    j.res_out = nullptr;
+}
+
+// Checks an input transform and copies it into a job (row offset `m0` of a chunked call).
+static int apply_input_op(Job &j, const hlq_input_op *op, int x_dtype, int m0) {
+    j.xop = HLQ_INPUT_PLAIN;
+    j.eps = 0.f;
+    j.x2 = nullptr;
+    j.gamma = nullptr;
+    j.res_out = nullptr;
+    if (!op || op->kind == HLQ_INPUT_PLAIN) return HLQ_OK;
+    if (op->kind != HLQ_INPUT_GATED_SILU && op->kind != HLQ_INPUT_ADD_RMSNORM) return HLQ_ERR_INVALID_ARGUMENT;
+    if (x_dtype != HLQ_F16) return HLQ_ERR_UNSUPPORTED;
+    if (j.k % 8) return HLQ_ERR_SHAPE;
+    if (op->kind == HLQ_INPUT_GATED_SILU && !op->d_second) return HLQ_ERR_INVALID_ARGUMENT;
+    if (op->kind == HLQ_INPUT_ADD_RMSNORM && !op->d_gamma) return HLQ_ERR_INVALID_ARGUMENT;
+    if (((uintptr_t)op->d_second | (uintptr_t)op->d_gamma | (uintptr_t)op->d_res_out) & 15) return HLQ_ERR_ALIGNMENT;
+    if (op->d_res_out && (op->d_res_out == j.x || op->d_res_out == op->d_second)) return HLQ_ERR_INVALID_ARGUMENT;
+    const size_t row = (size_t)m0 * j.k * 2;
+    j.xop = op->kind;
+    j.eps = op->eps;
+    j.x2 = op->d_second ? (const char *)op->d_second + row : nullptr;
+    j.gamma = (const uint16_t *)op->d_gamma;
+    j.res_out = op->kind == HLQ_INPUT_ADD_RMSNORM && op->d_res_out ? (uint16_t *)((char *)op->d_res_out + row) : nullptr;
+    return HLQ_OK;
 }
 
 int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
-                     void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+                     void *workspace, size_t workspace_bytes, cudaStream_t stream, const hlq_input_op *op) {
     if (w->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
     if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return HLQ_ERR_ALIGNMENT;
@@ -1205,6 +1364,9 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         a.y_is_f32 = y_dtype == HLQ_F32;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
+        rc = apply_input_op(a.single, op, x_dtype, m0);
+        if (rc) return rc;
+        a.one_row_passes = a.single.xop != HLQ_INPUT_PLAIN;
         int ctas = force_ctas > 0 ? force_ctas : di->sms;
         if ((long long)d.slices * d.duos < ctas) ctas = d.slices * d.duos;
         rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream);
@@ -1396,6 +1558,13 @@ int hlq_tp_comm_free(hlq_tp_comm *c) {
 int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,
                                  void *d_workspace, size_t workspace_bytes, const hlq_weight *w,
                                  hlq_tp_comm *comm, void *stream_) {
+    return hlq_linear_forward_allreduce_op(m, k, n, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, w, comm,
+                                           nullptr, stream_);
+}
+
+int hlq_linear_forward_allreduce_op(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,
+                                    void *d_workspace, size_t workspace_bytes, const hlq_weight *w,
+                                    hlq_tp_comm *comm, const hlq_input_op *op, void *stream_) {
     using namespace hlq;
     if (!w || !comm || m < 0) return HLQ_ERR_INVALID_ARGUMENT;
     if (k != w->k || n != w->n) return HLQ_ERR_SHAPE;
@@ -1422,6 +1591,9 @@ int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dty
     a.status = ws.status;
     a.dyn_smem = kLut8DynSmem;
     fill_job(a.single, w, d, d_x, x_dtype, d_y, y_dtype, ws.partial, ws.counters, 0);
+    rc = apply_input_op(a.single, op, x_dtype, 0);
+    if (rc) return rc;
+    a.one_row_passes = a.single.xop != HLQ_INPUT_PLAIN;
     int ctas = di->sms;
     if ((long long)d.slices * d.duos < ctas) ctas = d.slices * d.duos;
     return launch_lut8_any(w->q, d.gpw, a, dim3(ctas, m), (cudaStream_t)stream_);
@@ -1437,6 +1609,7 @@ struct hlq_group {
     long long total_units = 0;    // with the per-slice set-up share (launch_units)
     long long duo_units = 0;      // (slice, duo) pairs
     int seg_cost = 0;
+    bool one_row_passes = false;  // a member has an input transform
     std::vector<const hlq_weight *> weights;
     std::vector<hlq::Job> jobs_host;
     hlq::Job *d_jobs = nullptr;
@@ -1517,9 +1690,15 @@ int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weight
 
 int hlq_group_bind(hlq_group *g, const void *const *d_x, void *const *d_y, int x_dtype, int y_dtype,
                    void *stream) {
+    return hlq_group_bind_op(g, d_x, d_y, x_dtype, y_dtype, nullptr, stream);
+}
+
+int hlq_group_bind_op(hlq_group *g, const void *const *d_x, void *const *d_y, int x_dtype, int y_dtype,
+                      const hlq_input_op *ops, void *stream) {
     if (!g || !d_x || !d_y) return HLQ_ERR_INVALID_ARGUMENT;
     if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
     if (y_dtype != HLQ_F16 && y_dtype != HLQ_BF16 && y_dtype != HLQ_F32) return HLQ_ERR_UNSUPPORTED;
+    g->one_row_passes = false;
     for (int i = 0; i < g->count; ++i) {
         if (!d_x[i] || !d_y[i]) return HLQ_ERR_INVALID_ARGUMENT;
         if (((uintptr_t)d_x[i] & 15) || ((uintptr_t)d_y[i] & 3)) return HLQ_ERR_ALIGNMENT;
@@ -1527,6 +1706,9 @@ int hlq_group_bind(hlq_group *g, const void *const *d_x, void *const *d_y, int x
         g->jobs_host[i].y = d_y[i];
         g->jobs_host[i].x_dtype = x_dtype;
         g->jobs_host[i].y_dtype = y_dtype;
+        const int rc = hlq::apply_input_op(g->jobs_host[i], ops ? &ops[i] : nullptr, x_dtype, 0);
+        if (rc) return rc;
+        if (g->jobs_host[i].xop != HLQ_INPUT_PLAIN) g->one_row_passes = true;
     }
     // the table is small; a synchronous copy keeps the host vector free to change afterwards
     HLQ_CUDA(cudaMemcpyAsync(g->d_jobs, g->jobs_host.data(), sizeof(Job) * g->count, cudaMemcpyHostToDevice,
@@ -1557,6 +1739,7 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.status = (int *)g->d_scratch;
     a.dyn_smem = kLut8DynSmem;
     a.y_is_f32 = g->jobs_host[0].y_dtype == HLQ_F32;
+    a.one_row_passes = g->one_row_passes;
     int ctas = force_ctas > 0 ? force_ctas : di->sms;
     if (g->duo_units < ctas) ctas = (int)g->duo_units;
     return launch_lut8_any(g->q, g->gpw, a, dim3(ctas, m), (cudaStream_t)stream);

@@ -47,7 +47,8 @@ Workspace carve_workspace(void *base, int m, const StreamDims &d);
 
 // Kernels' launchers (defined in the .cu files).  All return an hlq_status.
 int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
-                     void *workspace, size_t workspace_bytes, cudaStream_t stream);
+                     void *workspace, size_t workspace_bytes, cudaStream_t stream,
+                     const hlq_input_op *op = nullptr);
 int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
                      cudaStream_t stream);
 int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, void *y,

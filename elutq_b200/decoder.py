@@ -60,7 +60,7 @@ class TPDecoder:
 
     def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
                  group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False,
-                 fused_glue: bool = True, quantized_lm_head: bool = True):
+                 fused_glue: bool = True, quantized_lm_head: bool = True, fused_inputs: bool = False):
         if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
         self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
@@ -110,11 +110,11 @@ class TPDecoder:
             L["u_o"] = torch.empty((1, c.ffn // world), dtype=dt, device=device)
             L["act"] = torch.empty((1, c.ffn // world), dtype=dt, device=device)
             L["d_o"] = torch.empty((1, c.hidden), dtype=dt, device=device)
+            L["r1"] = torch.empty((1, c.hidden), dtype=dt, device=device)   # residual stream after attention's add
+            L["r2"] = torch.empty((1, c.hidden), dtype=dt, device=device)   # ... after the MLP's add
             if grouped:
                 L["qkv"] = HLQGroup([L["q"], L["k"], L["v"]], max_m=1)
-                L["qkv"].bind([L["xn"]] * 3, [L["q_o"], L["k_o"], L["v_o"]])
                 L["gu"] = HLQGroup([L["gate"], L["up"]], max_m=1)
-                L["gu"].bind([L["xn2"]] * 2, [L["g_o"], L["u_o"]])
             self.layers.append(L)
         gen.manual_seed(seed + 100003)
         self.embed = (torch.randn((c.vocab, c.hidden), device=device, generator=gen) * 0.5).to(dt)
@@ -150,6 +150,37 @@ class TPDecoder:
             from .glue import DecodeAttention
             self.attn = DecodeAttention(self.hq, self.hkv, c.head_dim, c.ctx, c.rope_theta, device)
         self.x = torch.empty((1, c.hidden), dtype=dt, device=device)
+        self.xfinal = torch.empty((1, c.hidden), dtype=dt, device=device)
+        # norms and SiLU folded into the table build of the linear that follows them
+        self.fused_inputs = bool(fused_inputs and fused_glue and grouped and quantized_lm_head)
+        self._ops = []                       # keeps the op structs (and through them nothing else) alive
+        prev_delta, prev_res = None, self.x
+        for L in self.layers:
+            if not grouped:
+                break
+            if self.fused_inputs:
+                from .linear import input_op
+                n1 = input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=prev_res if prev_delta is not None else None,
+                              gamma=L["ln1"], res_out=L["r1"] if prev_delta is not None else None, eps=1e-5)
+                n1b = input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=prev_res if prev_delta is not None else None,
+                               gamma=L["ln1"], eps=1e-5)
+                src = prev_delta if prev_delta is not None else self.x
+                L["qkv"].bind([src] * 3, [L["q_o"], L["k_o"], L["v_o"]], ops=[n1, n1b, n1b])
+                res1 = L["r1"] if prev_delta is not None else self.x
+                n2 = input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=res1, gamma=L["ln2"], res_out=L["r2"], eps=1e-5)
+                n2b = input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=res1, gamma=L["ln2"], eps=1e-5)
+                L["gu"].bind([L["o_o"]] * 2, [L["g_o"], L["u_o"]], ops=[n2, n2b])
+                L["silu_op"] = input_op(_lib.HLQ_INPUT_GATED_SILU, second=L["u_o"])
+                self._ops += [n1, n1b, n2, n2b]
+                prev_delta, prev_res = L["d_o"], L["r2"]
+            else:
+                L["qkv"].bind([L["xn"]] * 3, [L["q_o"], L["k_o"], L["v_o"]])
+                L["gu"].bind([L["xn2"]] * 2, [L["g_o"], L["u_o"]])
+        if self.fused_inputs:
+            from .linear import input_op
+            self.final_op = input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=prev_res, gamma=self.norm,
+                                     res_out=self.xfinal, eps=1e-5)
+            self.final_src = prev_delta
         self.logit_max = torch.empty(2 * world, dtype=torch.float32, device=device)
         self.grouped = grouped
         self.graph = None
@@ -180,19 +211,48 @@ class TPDecoder:
         a, b = t[:, :c.head_dim // 2], t[:, c.head_dim // 2:]
         return torch.cat((a * self.cos - b * self.sin, a * self.sin + b * self.cos), dim=-1).half()
 
-    def _row_parallel(self, w, x, out):
-        """o / down: this rank's partial product, summed over the ranks."""
+    def _row_parallel(self, w, x, out, op=None):
+        """o / down: this rank's partial product, summed over the ranks (`op`: input transform)."""
         if self.comm is not None:
-            self.comm.forward(x, w, self.ws, out)
+            self.comm.forward(x, w, self.ws, out, op=op)
             return
-        self._linear(w, x, out)
+        if op is not None:
+            from .linear import linear_forward_op
+            linear_forward_op(x, w, self.ws, out, op)
+        else:
+            self._linear(w, x, out)
         if self.world > 1:
             torch.distributed.all_reduce(out, group=self.group)
 
     def step_eager(self, token=None):
         """One decode step on `token` (None: the id already in self.token); returns the next
         token id (greedy) as a device tensor."""
+        if self.fused_inputs:
+            return self._step_fused_inputs(token)
         return self._step_fused(token) if self.fused_glue else self._step_torch(token)
+
+    def _step_fused_inputs(self, token):
+        """5 launches per layer: both norms (with their residual adds) and the gated SiLU run
+        inside the table build of the linear they feed (hlq_input_op)."""
+        from . import glue
+        from .linear import linear_forward_op
+        c = self.cfg
+        if token is not None:
+            self.token.fill_(int(token))
+        torch.index_select(self.embed, 0, self.token, out=self.x)
+        stream = torch.cuda.current_stream(self.dev).cuda_stream
+        for L in self.layers:
+            _lib.check(_lib.lib().hlq_group_forward(L["qkv"].handle, 1, stream), "hlq_group_forward")
+            self.attn.forward(L["q_o"].view(self.hq, c.head_dim), L["k_o"].view(self.hkv, c.head_dim),
+                              L["v_o"].view(self.hkv, c.head_dim), L["kc"], L["vc"], self.position,
+                              out=L["att"].view(self.hq, c.head_dim))
+            self._row_parallel(L["o"], L["att"], L["o_o"])
+            _lib.check(_lib.lib().hlq_group_forward(L["gu"].handle, 1, stream), "hlq_group_forward")
+            self._row_parallel(L["down"], L["g_o"], L["d_o"], op=L["silu_op"])
+        linear_forward_op(self.final_src, self.lm_w, self.ws, self.logits, self.final_op)
+        glue.argmax(self.logits.view(-1), self.next_index, self.next_value)
+        self.last_logits = self.logits
+        return self._pick(self.next_value, self.next_index)
 
     def _groups_or_linears(self, L, which, stream):
         if self.grouped:
@@ -308,9 +368,12 @@ class TPDecoder:
         """Kernels of this package in one step (the embedding copy, the lm_head product and the
         collectives are library calls and not counted)."""
         per_layer = (2 if self.grouped else 5) + 2          # qkv, gate/up (+ o, down below)
-        if self.fused_glue:
+        if self.fused_inputs:
+            per_layer += 1                                  # attention
+        elif self.fused_glue:
             per_layer += 4                                  # two norms, attention, gated silu
-        return len(self.layers) * per_layer + (2 if self.fused_glue else 0) + (1 if self.lm_w is not None else 0)
+        tail = 1 if self.fused_inputs else (2 if self.fused_glue else 0)      # (final norm,) argmax
+        return len(self.layers) * per_layer + tail + (1 if self.lm_w is not None else 0)
 
     def hidden_after_step(self):
-        return self.x
+        return self.xfinal if self.fused_inputs else self.x

@@ -147,6 +147,32 @@ def workspace_bytes(m: int, k: int, n: int, bits: int, groupsize: int) -> int:
     return int(_lib.lib().hlq_workspace_bytes(m, k, n, bits, groupsize))
 
 
+def input_op(kind: int = 0, second: Optional[torch.Tensor] = None, gamma: Optional[torch.Tensor] = None,
+             res_out: Optional[torch.Tensor] = None, eps: float = 0.0) -> "_lib.InputOp":
+    """An hlq_input_op: HLQ_INPUT_GATED_SILU (x = gate, second = up) or HLQ_INPUT_ADD_RMSNORM
+    (second = residual to add or None, gamma, optional res_out).  The caller keeps the tensors
+    alive for as long as the op is used."""
+    for t in (second, gamma, res_out):
+        if t is not None and (not t.is_cuda or t.dtype != torch.float16 or not t.is_contiguous()):
+            raise ValueError("input-transform tensors must be contiguous CUDA fp16")
+    ptr = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+    return _lib.InputOp(kind, float(eps), ptr(second), ptr(gamma), ptr(res_out))
+
+
+def linear_forward_op(x: torch.Tensor, weight: HLQWeight, workspace: Workspace, out: torch.Tensor,
+                      op: "_lib.InputOp") -> torch.Tensor:
+    """LUT GEMV (m <= 16) with an input transform applied while its tables are built
+    (hlq_linear_forward_op)."""
+    i = weight.info
+    m = x.numel() // i.in_channel
+    with torch.cuda.device(x.device):
+        st = _lib.lib().hlq_linear_forward_op(m, i.in_channel, i.out_channel, x.data_ptr(), _DTYPES[x.dtype],
+                                              out.data_ptr(), _DTYPES[out.dtype], workspace.ptr, workspace.nbytes,
+                                              weight.handle, ctypes.byref(op), _stream_ptr(x.device))
+    _lib.check(st, "hlq_linear_forward_op")
+    return out
+
+
 def linear_forward(x: torch.Tensor, weight: HLQWeight, workspace: Workspace,
                    out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
                    impl: int = _lib.IMPL_AUTO) -> torch.Tensor:
@@ -197,8 +223,9 @@ class HLQGroup:
         self.max_m = max_m
         self._bound = None
 
-    def bind(self, xs, ys):
-        """xs[i]: [m, k_i] fp16/bf16 CUDA tensors; ys[i]: [m, n_i] outputs (one dtype each)."""
+    def bind(self, xs, ys, ops=None):
+        """xs[i]: [m, k_i] fp16/bf16 CUDA tensors; ys[i]: [m, n_i] outputs (one dtype each);
+        ops[i]: optional input transform of member i (see input_op)."""
         if len(xs) != len(self.weights) or len(ys) != len(self.weights):
             raise ValueError("one x and one y per member")
         for x, y, w in zip(xs, ys, self.weights):
@@ -208,9 +235,14 @@ class HLQGroup:
                 raise ValueError("x and y must be contiguous")
         xa = (ctypes.c_void_p * len(xs))(*[x.data_ptr() for x in xs])
         ya = (ctypes.c_void_p * len(ys))(*[y.data_ptr() for y in ys])
+        oa = None
+        if ops is not None:
+            if len(ops) != len(self.weights):
+                raise ValueError("one op per member")
+            oa = (_lib.InputOp * len(ops))(*ops)
         with torch.cuda.device(self.device):
-            _lib.check(_lib.lib().hlq_group_bind(self._h, xa, ya, _DTYPES[xs[0].dtype], _DTYPES[ys[0].dtype],
-                                                 _stream_ptr(self.device)), "hlq_group_bind")
+            _lib.check(_lib.lib().hlq_group_bind_op(self._h, xa, ya, _DTYPES[xs[0].dtype], _DTYPES[ys[0].dtype],
+                                                    oa, _stream_ptr(self.device)), "hlq_group_bind_op")
         self._bound = (list(xs), list(ys))    # keeps the tensors alive
 
     def forward(self, m: int = 1):

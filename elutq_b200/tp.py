@@ -134,15 +134,17 @@ class FusedAllReduceComm:
     def handle(self):
         return self._h
 
-    def forward(self, x, weight, workspace, out):
-        """out <- sum over ranks of x . W_hat[:, this rank's channels]^T (+ bias of rank 0)."""
-        import torch
+    def forward(self, x, weight, workspace, out, op=None):
+        """out <- sum over ranks of x_eff . W_hat[:, this rank's channels]^T (+ bias of rank 0);
+        `op`: optional input transform (linear.input_op)."""
+        import ctypes
         from .linear import _DTYPES, _stream_ptr
         i = weight.info
         m = x.shape[0]
-        st = _lib.lib().hlq_linear_forward_allreduce(
+        st = _lib.lib().hlq_linear_forward_allreduce_op(
             m, i.in_channel, i.out_channel, x.data_ptr(), _DTYPES[x.dtype], out.data_ptr(), _DTYPES[out.dtype],
-            workspace.ptr, workspace.nbytes, weight.handle, self._h, _stream_ptr(x.device))
+            workspace.ptr, workspace.nbytes, weight.handle, self._h, ctypes.byref(op) if op is not None else None,
+            _stream_ptr(x.device))
         _lib.check(st, "hlq_linear_forward_allreduce")
         return out
 

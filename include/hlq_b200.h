@@ -254,6 +254,46 @@ int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dty
                                  int y_dtype, void *d_workspace, size_t workspace_bytes,
                                  const hlq_weight *w, hlq_tp_comm *comm, void *stream);
 
+/* ---- input transforms fused into the LUT GEMV ------------------------------------------
+ *
+ * The GEMV reads its activations slice by slice to build its lookup tables; an elementwise
+ * op (or a norm) in front of a linear can be applied right there instead of in a kernel of
+ * its own.  fp16 activations, streaming-layout weights, m <= 16 (one row of x per pass).
+ *   HLQ_INPUT_GATED_SILU:  x_eff = fp16(second * x / (1 + exp(-x)))       x = gate, second = up
+ *       = gated_silu (C++/ops/src/arm/arm_activation.cpp:22-52) in front of down_proj
+ *   HLQ_INPUT_ADD_RMSNORM: t = x + second (second may be NULL); res_out = fp16(t) (may be
+ *       NULL, must not alias x or second); x_eff = fp16(fp16(t) * gamma / sqrt(mean(t^2) + eps))
+ *       = launch_pre_rms_norm / launch_rms_norm (C++/ops/src/arm/arm_rmsnorm.cpp:25-41, 68-85)
+ *       in front of q/k/v, gate/up or lm_head.
+ * The values the tables see are rounded to fp16 exactly where the separate kernels
+ * (hlq_gated_silu, hlq_rmsnorm) round. */
+typedef enum hlq_input_kind {
+    HLQ_INPUT_PLAIN = 0,
+    HLQ_INPUT_GATED_SILU = 1,
+    HLQ_INPUT_ADD_RMSNORM = 2
+} hlq_input_kind;
+typedef struct hlq_input_op {
+    int kind;               /* hlq_input_kind */
+    float eps;              /* ADD_RMSNORM */
+    const void *d_second;   /* fp16 [m][k] */
+    const void *d_gamma;    /* ADD_RMSNORM: fp16 [k] */
+    void *d_res_out;        /* ADD_RMSNORM: fp16 [m][k] or NULL */
+} hlq_input_op;
+/* hlq_linear_forward with an input transform (op NULL or PLAIN: the same as hlq_linear_forward
+ * restricted to the LUT GEMV). */
+int hlq_linear_forward_op(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,
+                          void *d_workspace, size_t workspace_bytes, const hlq_weight *w,
+                          const hlq_input_op *op, void *stream);
+/* hlq_linear_forward_allreduce with an input transform. */
+int hlq_linear_forward_allreduce_op(int m, int k, int n, const void *d_x, int x_dtype, void *d_y,
+                                    int y_dtype, void *d_workspace, size_t workspace_bytes,
+                                    const hlq_weight *w, hlq_tp_comm *comm, const hlq_input_op *op,
+                                    void *stream);
+/* hlq_group_bind with one input transform per member (ops NULL: none).  Members that share an
+ * ADD_RMSNORM input should name d_res_out in one of them only. */
+int hlq_group_bind_op(hlq_group *g, const void *const *d_x, void *const *d_y, int x_dtype,
+                      int y_dtype, const hlq_input_op *ops, void *stream);
+
 /* ---- decoder glue between the linears (fp16, device pointers, one token) --------------
  *
  * The per-token ops the reference's model runs between two quantized linears

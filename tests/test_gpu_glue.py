@@ -153,3 +153,102 @@ def test_attention_position_comes_from_device_memory_and_is_checked():
     with pytest.raises(_lib.HlqError):                                   # group of 16 query heads
         glue.DecodeAttention(16, 1, 128, 64, 1e4, DEV).forward(z(16, d), z(1, d), z(1, d), z(64, 1, d), z(64, 1, d),
                                                                 position)
+
+
+# ---- input transforms fused into the LUT GEMV's table build ---------------------------------
+
+def _linear_case(n, k, q=2, g=128, seed=0):
+    from elutq_b200 import format as F, linear as lm
+    from oracle import hlq_oracle as O
+    d = O.synth_linear(n, k, q, g, m=1, seed=seed)
+    lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], None, g)
+    w = lm.HLQWeight.from_export(lin, device=0)
+    ws = lm.Workspace(lm.workspace_bytes(1, k, n, q, g), torch.device(DEV))
+    return d, w, ws, lm
+
+
+@pytest.mark.parametrize("n,k", [(256, 1024), (96, 14336), (1024, 62 * 128)])
+def test_gated_silu_inside_the_gemv_equals_the_two_kernels(n, k):
+    d, w, ws, lm = _linear_case(n, k, seed=n + k)
+    rng = np.random.default_rng(n)
+    gate = t16((2 * rng.standard_normal((1, k))).astype(np.float16))
+    up = t16(rng.standard_normal((1, k)).astype(np.float16))
+    ref = lm.linear_forward(glue.gated_silu(gate, up), w, ws, out_dtype=torch.float32)
+    out = torch.empty((1, n), dtype=torch.float32, device=DEV)
+    lm.linear_forward_op(gate, w, ws, out, lm.input_op(_lib.HLQ_INPUT_GATED_SILU, second=up))
+    torch.cuda.synchronize()
+    assert ws.kernel_status() == 0
+    # the tables see the same fp16 activations: equal up to the order of the slice sums
+    err = (out - ref).abs().max() / ref.abs().max()
+    assert err <= 1e-6, float(err)
+
+
+@pytest.mark.parametrize("n,k,with_res", [(256, 4096, True), (1024, 8192, True), (320, 1024, False), (64, 640, True)])
+def test_add_rmsnorm_inside_the_gemv_equals_the_two_kernels(n, k, with_res):
+    d, w, ws, lm = _linear_case(n, k, seed=n + k + 1)
+    rng = np.random.default_rng(k)
+    x = t16(rng.standard_normal((1, k)).astype(np.float16))
+    res = t16(rng.standard_normal((1, k)).astype(np.float16)) if with_res else None
+    gamma = t16((1 + 0.1 * rng.standard_normal(k)).astype(np.float16))
+    if with_res:
+        xn, r_ref = glue.rmsnorm(x, gamma, 1e-5, residual=res)
+    else:
+        xn, r_ref = glue.rmsnorm(x, gamma, 1e-5), None
+    ref = lm.linear_forward(xn, w, ws, out_dtype=torch.float32)
+    out = torch.empty((1, n), dtype=torch.float32, device=DEV)
+    r_out = torch.zeros((1, k), dtype=torch.float16, device=DEV) if with_res else None
+    op = lm.input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=res, gamma=gamma, res_out=r_out, eps=1e-5)
+    lm.linear_forward_op(x, w, ws, out, op)
+    torch.cuda.synchronize()
+    assert ws.kernel_status() == 0
+    if with_res:
+        assert torch.equal(r_out, r_ref)          # the residual stream: bit-exact
+    # 1/rms is summed in another order than in the stand-alone kernel: a few normalized
+    # activations may round to the neighbouring fp16 value
+    err = (out - ref).abs().max() / ref.abs().max()
+    assert err <= 5e-4, float(err)
+    # and against the oracle of the whole chain
+    from oracle import hlq_oracle as O
+    xo, _ = GO.rmsnorm(x.cpu().numpy(), gamma.cpu().numpy(), 1e-5, res.cpu().numpy() if with_res else None)
+    yo = O.hlq_linear(xo, d["w_quant"], d["w_scale"], d["w_zero"], 128, None)
+    assert O.normwise_error(out.cpu().numpy(), yo) <= 1e-3
+
+
+def test_group_members_with_input_transforms():
+    from elutq_b200 import linear as lm
+    k = 2048
+    d1, w1, ws, _ = _linear_case(512, k, seed=5)
+    d2, w2, _, _ = _linear_case(128, k, seed=6)
+    rng = np.random.default_rng(3)
+    x = t16(rng.standard_normal((1, k)).astype(np.float16))
+    res = t16(rng.standard_normal((1, k)).astype(np.float16))
+    gamma = t16((1 + 0.1 * rng.standard_normal(k)).astype(np.float16))
+    xn, r_ref = glue.rmsnorm(x, gamma, 1e-5, residual=res)
+    ws2 = lm.Workspace(lm.workspace_bytes(1, k, 512, 2, 128), torch.device(DEV))
+    refs = [lm.linear_forward(xn, w, ws2) for w in (w1, w2)]
+    ys = [torch.empty((1, 512), dtype=torch.float16, device=DEV), torch.empty((1, 128), dtype=torch.float16, device=DEV)]
+    r_out = torch.zeros_like(x)
+    grp = lm.HLQGroup([w1, w2], max_m=1)
+    grp.bind([x, x], ys, ops=[lm.input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=res, gamma=gamma, res_out=r_out, eps=1e-5),
+                              lm.input_op(_lib.HLQ_INPUT_ADD_RMSNORM, second=res, gamma=gamma, eps=1e-5)])
+    grp.forward(1)
+    torch.cuda.synchronize()
+    assert grp.kernel_status() == 0
+    assert torch.equal(r_out, r_ref)
+    for y, r in zip(ys, refs):
+        assert (y.float() - r.float()).abs().max() / r.float().abs().max() <= 2e-3
+
+
+def test_input_transform_argument_errors():
+    d, w, ws, lm = _linear_case(64, 512)
+    x = torch.zeros((1, 512), dtype=torch.float16, device=DEV)
+    out = torch.empty((1, 64), dtype=torch.float16, device=DEV)
+    with pytest.raises(_lib.HlqError):          # gated SiLU without its second input
+        lm.linear_forward_op(x, w, ws, out, lm.input_op(_lib.HLQ_INPUT_GATED_SILU))
+    with pytest.raises(_lib.HlqError):          # norm without gamma
+        lm.linear_forward_op(x, w, ws, out, lm.input_op(_lib.HLQ_INPUT_ADD_RMSNORM))
+    with pytest.raises(_lib.HlqError):          # res_out may not alias the input
+        lm.linear_forward_op(x, w, ws, out, lm.input_op(_lib.HLQ_INPUT_ADD_RMSNORM, gamma=x, res_out=x))
+    with pytest.raises(_lib.HlqError):          # bf16 activations: not with a transform
+        lm.linear_forward_op(x.bfloat16(), w, ws, out, lm.input_op(_lib.HLQ_INPUT_GATED_SILU, second=x))
+

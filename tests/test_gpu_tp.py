@@ -132,7 +132,7 @@ def test_one_gpu_decoder_own_glue_equals_torch_glue():
     sys.path.insert(0, ROOT)
     from elutq_b200.decoder import PRESETS, TPDecoder
     dev = torch.device("cuda", 0)
-    a = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=11, fused_glue=True)
+    a = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=11, fused_glue=True, fused_inputs=False)
     b = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=11, fused_glue=False)
     ta, tb = a.step_eager(7), b.step_eager(7)
     torch.cuda.synchronize()
@@ -152,5 +152,29 @@ def test_one_gpu_decoder_own_glue_equals_torch_glue():
     g.replay()
     torch.cuda.synchronize()
     assert a.attn.status() == 0
+    assert (a.hidden_after_step().float() - xb).abs().max() / xb.abs().max() <= 4e-3
+
+
+def test_one_gpu_decoder_norms_and_silu_inside_the_gemv():
+    """5 launches per layer (input transforms) against 8 (separate glue kernels)."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    sys.path.insert(0, ROOT)
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    dev = torch.device("cuda", 0)
+    a = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=13, fused_inputs=True)
+    b = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=13, fused_inputs=False)
+    assert a.fused_inputs and not b.fused_inputs
+    assert a.launches_per_step() < b.launches_per_step()
+    ta, tb = a.step_eager(7), b.step_eager(7)
+    torch.cuda.synchronize()
+    xa, xb = a.hidden_after_step().float(), b.hidden_after_step().float()
+    assert (xa - xb).abs().max() / xb.abs().max() <= 4e-3
+    la, lb = a.last_logits.float(), b.last_logits.float()
+    assert (la - lb).abs().max() / lb.abs().max() <= 1e-2
+    g = a.capture(7)
+    a.token.fill_(7)
+    g.replay()
+    torch.cuda.synchronize()
     assert (a.hidden_after_step().float() - xb).abs().max() / xb.abs().max() <= 4e-3
 
