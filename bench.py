@@ -402,7 +402,16 @@ def run_decode(args):
     cfg = dataclasses.replace(cfg, bits=args.bits, groupsize=args.groupsize)
     dec = TPDecoder(cfg, dev, rank, world, seed=args.seed, grouped=not args.ungrouped,
                     fused_allreduce=args.fused_allreduce, fused_glue=not args.torch_glue)
-    graph = dec.capture(1)
+    if args.no_graph:
+        # eager steps (for a profiler's launch list; the numbers then include host launch gaps)
+        class _Eager:
+            def replay(self):
+                dec.step_eager(None)
+        for _ in range(2):
+            dec.step_eager(1)
+        graph = _Eager()
+    else:
+        graph = dec.capture(1)
 
     def barrier():
         if world > 1:
@@ -452,7 +461,7 @@ def run_decode(args):
                        "glue": ("PyTorch ops (norm, rope, attention, silu, lm_head) inside one CUDA graph"
                                 if args.torch_glue else
                                 "own kernels (residual+RMSNorm, RoPE+KV append+attention, gated SiLU, argmax), "
-                                "w4g128 HLQ lm_head, one CUDA graph"),
+                                "w4g128 HLQ lm_head, " + ("eager launches" if args.no_graph else "one CUDA graph")),
                        "collectives": ("all-reduce fused into the o and down GEMV kernels (peer stores over NVLink)"
                                        if args.fused_allreduce else "NCCL all-reduce after o and down")
                                       + ", NCCL all-gather of the arg-max"},

@@ -41,9 +41,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#ifdef HLQ_GEMV_PROF
-#include <cstdio>
-#endif
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -551,11 +548,6 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     return (const uint16_t *)jb.x + (long long)w.mrow * jb.k + (long long)s * kSliceK;
 }
 
-#ifdef HLQ_GEMV_PROF
-constexpr unsigned kProfSlots = 8192;
-__device__ unsigned long long g_prof[kProfSlots][8];
-__device__ unsigned g_prof_count;
-#endif
 
 // R = rows of x one pass serves: 1, or 2 with half2 table entries {row, row + 1}.
 // XOP: the instantiation that applies the jobs' input transforms (one-row passes only), kept
@@ -583,20 +575,6 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
     Seg *ring = (Seg *)(aux + kAuxSeg);
     const uint32_t mb_desc = aux_u32 + kAuxMbarDesc, mb_x = aux_u32 + kAuxMbarX;
 
-#ifdef HLQ_GEMV_PROF
-    __shared__ unsigned prof_slot;
-    if (tid == 0) {
-        prof_slot = atomicAdd(&g_prof_count, 1u) % kProfSlots;
-        unsigned long long t_;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
-        g_prof[prof_slot][0] = t_;
-        g_prof[prof_slot][7] = blockIdx.x;
-    }
-#define GT_MARK(idx) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
-        g_prof[prof_slot][idx] = t_; }
-#else
-#define GT_MARK(idx)
-#endif
     pdl_launch_dependents();
     if (tid == 0) {
         mbar_init(mb_desc, 1);
@@ -794,7 +772,6 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
             }
         }
         if (*fail && ftid == 0) atomicExch(a.status, 1);
-        if (ftid == 0) GT_MARK(5);
         return;
     }
 
@@ -850,7 +827,6 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
     for (int i = 0;; ++i) {
         const int slot = i & 1;
         named_bar_sync<kBarConsumers, kConsumers>();     // everyone is done with the old table
-        if (tid == 0 && i == 0) GT_MARK(1);
         if (i == 0) pdl_wait();   // orders this thread's reads and writes after the previous grid
         if (XOP && cur_xop == HLQ_INPUT_ADD_RMSNORM && cur_job != rms_job) {
             // 1 / rms of the whole row t = x + x2, once per job and CTA (the rows sit in L2)
@@ -883,7 +859,6 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
             named_bar_sync<kBarConsumers, kConsumers>();     // red[] may be rewritten by the next job
         }
         if (!mbar_wait_bounded(mb_x + 8 * slot, (i >> 1) & 1)) *fail = 1;
-        if (tid == 0 && i == 0) GT_MARK(2);
         const uint16_t *xs = (const uint16_t *)(aux + kX) + slot * (R * kSliceK);
         // group sums (warps 0..R-1) and the 64 tables of 256 subset sums (all consumer warps)
         const uint16_t *xs2 = (const uint16_t *)(aux + kAuxX2) + slot * kSliceK;     // input transform only
@@ -968,7 +943,6 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         }
         named_bar_sync<kBarConsumers, kConsumers>();
         asm volatile("" ::: "memory");
-        if (tid == 0 && i == 0) GT_MARK(3);
 
         float xsu[GPW], xsu1[GPW];
 #pragma unroll
@@ -1026,7 +1000,6 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         named_bar_arrive_dyn(kBarSegDone + slot, kThreads);
         if (!nx.live) break;
     }
-    if (tid == 0) GT_MARK(4);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1857,14 +1830,4 @@ int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
 
 }  // namespace hlq
 
-#ifdef HLQ_GEMV_PROF
-extern "C" int hlq_dbg_prof_read(void *host_out, unsigned *count) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(count, hlq::g_prof_count, sizeof(unsigned));
-    cudaMemcpyFromSymbol(host_out, hlq::g_prof, sizeof(unsigned long long) * hlq::kProfSlots * 8);
-    unsigned zero = 0;
-    cudaMemcpyToSymbol(hlq::g_prof_count, &zero, sizeof(unsigned));
-    return 0;
-}
-#endif
 
