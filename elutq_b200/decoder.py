@@ -364,6 +364,33 @@ class TPDecoder:
             self.step_eager(None)          # the graph reads the token id from self.token
         return self.graph
 
+    def generate(self, first_token: int, n_tokens: int, start_position: int, use_graph: bool = True):
+        """Greedy decoding of `n_tokens` tokens from `start_position` on (own glue kernels only:
+        the position and the token id live in device memory, so ONE captured graph serves every
+        step; between two replays the position is incremented and the chosen token fed back,
+        both on the device).  Returns the token ids as a list."""
+        if not self.fused_glue:
+            raise RuntimeError("generate() needs the package's glue kernels (fused_glue=True)")
+        if start_position < 0 or start_position + n_tokens > self.cfg.ctx:
+            raise ValueError("positions leave the KV cache")
+        self.position.fill_(start_position)
+        self.token.fill_(int(first_token))
+        if use_graph and self.graph is None:
+            keep = self.position.clone()
+            self.capture(first_token)
+            self.position.copy_(keep)
+            self.token.fill_(int(first_token))
+        out = []
+        for _ in range(n_tokens):
+            if use_graph:
+                self.graph.replay()
+            else:
+                self.step_eager(None)
+            self.token.copy_(self.next_token.view(1))
+            self.position.add_(1)
+            out.append(self.next_token.view(1).clone())
+        return [int(t) for t in torch.cat(out).tolist()]
+
     def launches_per_step(self) -> int:
         """Kernels of this package in one step (the embedding copy, the lm_head product and the
         collectives are library calls and not counted)."""

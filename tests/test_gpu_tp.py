@@ -178,3 +178,26 @@ def test_one_gpu_decoder_norms_and_silu_inside_the_gemv():
     torch.cuda.synchronize()
     assert (a.hidden_after_step().float() - xb).abs().max() / xb.abs().max() <= 4e-3
 
+
+def test_generate_with_one_graph_equals_eager_steps():
+    """Position and token id live in device memory: one captured graph decodes every step."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    sys.path.insert(0, ROOT)
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    dev = torch.device("cuda", 0)
+    a = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=21)
+    b = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=21)
+    ta = a.generate(3, 6, start_position=100, use_graph=True)
+    tb = b.generate(3, 6, start_position=100, use_graph=False)
+    assert ta == tb and len(ta) == 6
+    assert int(a.position.item()) == 106 and a.attn.status() == 0
+    # the cache rows 100..105 were written by the steps (equal up to the order of the GEMVs'
+    # slice sums, which can move an fp16 rounding), nothing beyond them was touched
+    for La, Lb in zip(a.layers, b.layers):
+        assert (La["kc"][100:106].float() - Lb["kc"][100:106].float()).abs().max() <= 3e-2
+        assert torch.equal(La["kc"][106:], Lb["kc"][106:])
+        assert torch.equal(La["vc"][106:], Lb["vc"][106:])
+    with pytest.raises(ValueError):
+        a.generate(1, 10, start_position=250)
+
