@@ -88,7 +88,7 @@ SIGNATURES = {
     "hlq_gated_silu": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "hlq_argmax": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "hlq_attention_workspace_bytes": (c_size_t, [c_int] * 4),
-    "hlq_rope_cache_attention": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_float, c_float, c_void_p, c_void_p,
+    "hlq_rope_cache_attention": (c_int, [c_void_p] * 6 + [c_int] * 5 + [c_float, c_float, c_void_p, c_void_p,
                                                                        c_size_t, c_void_p]),
     "hlq_last_error_string": (c_char_p, [c_int]),
     "hlq_last_cuda_error": (c_int, []),
@@ -103,6 +103,7 @@ class InputOp(ctypes.Structure):
 
 
 HLQ_INPUT_PLAIN, HLQ_INPUT_GATED_SILU, HLQ_INPUT_ADD_RMSNORM = 0, 1, 2
+HLQ_KV_POSITION_MAJOR, HLQ_KV_HEAD_MAJOR = 0, 1
 
 _LIB = None
 

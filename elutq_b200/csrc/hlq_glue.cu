@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+
 #include <stdint.h>
 
 #include "hlq_internal.h"
@@ -210,7 +211,8 @@ constexpr int kMaxSplits = 64;      // kMaxGroup * kMaxSplits floats fit the til
 
 struct AttnArgs {
     const __half *q, *k, *v;      // this token's projections: [head_q][D], [head_kv][D], [head_kv][D]
-    __half *kcache, *vcache;      // [max_ctx][head_kv][D]
+    __half *kcache, *vcache;      // [max_ctx][head_kv][D] or [head_kv][max_ctx][D]
+    long long pos_stride, head_stride;   // elements between two positions / two kv heads of a cache
     const int *position;          // device: position of this token = number of cached tokens
     __half *out;                  // [head_q][D]
     float *partial;               // [head_kv][splits][G][D + 2]
@@ -220,8 +222,15 @@ struct AttnArgs {
     float rotary_base, scale;
 };
 
-template <int D>
-__global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
+// S threads share a position in the score phase (each takes D/S channels of the K row) and
+// S groups of threads share the positions of a tile in the weighted sum of V: with one warp
+// per scheduler the kernel was bound by the latency of its own instruction chains.
+template <int D, int S>
+__global__ void __launch_bounds__(D *S) attention_decode_kernel(const AttnArgs a) {
+    constexpr int T = D * S;               // threads
+    constexpr int KV = D / 8 / S;          // 16-byte loads per thread for its part of a K row / of the V tile
+    static_assert(S == 1 || S == 2 || S == 4, "threads per position");
+    static_assert(KV >= 1 && (S - 1) * kMaxGroup * D * 4 <= D * D * 2, "the partial sums reuse the V tile");
     __shared__ __align__(16) float qs[kMaxGroup][D];       // roped queries times scale
     __shared__ __align__(16) float pw[D][kMaxGroup];       // scores, then weights, of a tile
     __shared__ __align__(16) __half vs[D * D];             // the V tile: [position][channel]
@@ -239,7 +248,8 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
     const int nkv = pos + 1;
     const int per = (nkv + nsplit - 1) / nsplit;
     const int t0 = split * per, t1 = min(nkv, t0 + per);
-    const size_t row_stride = (size_t)a.head_kv * D;
+    const size_t row_stride = (size_t)a.pos_stride;
+    const size_t head_off = (size_t)hk * (size_t)a.head_stride;
 
     // RoPE: pair (j, j + D/2), angle = pos * base^(-2j/D), results rounded to fp16 as stored
     if (tid < D / 2) {
@@ -255,13 +265,13 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
         if (pos >= t0 && pos < t1) {             // this CTA's share holds the new position: append
             const __half *kp = a.k + (size_t)hk * D;
             const float k1 = __half2float(kp[tid]), k2 = __half2float(kp[tid + D / 2]);
-            __half *kc = a.kcache + (size_t)pos * row_stride + (size_t)hk * D;
+            __half *kc = a.kcache + (size_t)pos * row_stride + head_off;
             kc[tid] = __float2half_rn(k1 * cs - k2 * sn);
             kc[tid + D / 2] = __float2half_rn(k1 * sn + k2 * cs);
         }
-    } else if (pos >= t0 && pos < t1) {
+    } else if (tid < D && pos >= t0 && pos < t1) {
         const int j = tid - D / 2;
-        __half *vc = a.vcache + (size_t)pos * row_stride + (size_t)hk * D;
+        __half *vc = a.vcache + (size_t)pos * row_stride + head_off;
         const __half *vp = a.v + (size_t)hk * D;
         vc[j] = vp[j];
         vc[j + D / 2] = vp[j + D / 2];
@@ -276,31 +286,33 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
     for (int g = 0; g < kMaxGroup; ++g) acc[g] = 0.f;
     __syncthreads();
 
+    const int sp = tid / S, part = tid % S;      // score phase: position of the tile, part of its row
+    const int ch = tid % D, pg = tid / D;        // V phase: channel, group of positions
     for (int tile = t0; tile < t1; tile += D) {
         const int ntile = min(D, t1 - tile);
         // All global loads of the tile are issued before anything is computed: this thread's
-        // K row (D/8 16-byte loads) and its share of the V tile (D/8 more, coalesced).
-        uint4 kreg[D / 8], vreg[D / 8];
-        if (tid < ntile) {
-            const uint4 *kr = (const uint4 *)(a.kcache + (size_t)(tile + tid) * row_stride + (size_t)hk * D);
+        // part of a K row and its share of the V tile (both coalesced).
+        uint4 kreg[KV], vreg[KV];
+        if (sp < ntile) {
+            const uint4 *kr = (const uint4 *)(a.kcache + (size_t)(tile + sp) * row_stride + head_off) + part * KV;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) kreg[c] = kr[c];
+            for (int c = 0; c < KV; ++c) kreg[c] = kr[c];
         }
 #pragma unroll
-        for (int u = 0; u < D / 8; ++u) {
-            const int idx = tid + u * D, t = idx / (D / 8), ch = idx % (D / 8);
+        for (int u = 0; u < KV; ++u) {
+            const int idx = tid + u * T, t = idx / (D / 8), c8 = idx % (D / 8);
             vreg[u] = make_uint4(0u, 0u, 0u, 0u);
             if (t < ntile)
-                vreg[u] = *(const uint4 *)(a.vcache + (size_t)(tile + t) * row_stride + (size_t)hk * D + 8 * ch);
+                vreg[u] = *(const uint4 *)(a.vcache + (size_t)(tile + t) * row_stride + head_off + 8 * c8);
         }
-        // scores: thread = position
+        // scores: S threads per position, then a shuffle reduction among them
         {
             float s[kMaxGroup];
 #pragma unroll
             for (int g = 0; g < kMaxGroup; ++g) s[g] = 0.f;
-            if (tid < ntile) {
+            if (sp < ntile) {
 #pragma unroll
-                for (int c = 0; c < D / 8; ++c) {
+                for (int c = 0; c < KV; ++c) {
                     const __half2 *kh = (const __half2 *)&kreg[c];
                     float kf[8];
 #pragma unroll
@@ -309,27 +321,33 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
                         kf[2 * e] = f.x;
                         kf[2 * e + 1] = f.y;
                     }
+                    const int c0 = 8 * (part * KV + c);
 #pragma unroll
                     for (int g = 0; g < kMaxGroup; ++g) {
                         if (g < G) {
-                            const float4 qa = *(const float4 *)&qs[g][8 * c], qb = *(const float4 *)&qs[g][8 * c + 4];
+                            const float4 qa = *(const float4 *)&qs[g][c0], qb = *(const float4 *)&qs[g][c0 + 4];
                             s[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x +
                                     kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
                         }
                     }
                 }
-            } else {
-#pragma unroll
-                for (int g = 0; g < kMaxGroup; ++g) s[g] = -INFINITY;
             }
 #pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) pw[tid][g] = s[g];
+            for (int g = 0; g < kMaxGroup; ++g) {
+#pragma unroll
+                for (int dd = 1; dd < S; dd <<= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], dd);
+                if (sp >= ntile) s[g] = -INFINITY;
+            }
+            if (part == 0) {
+#pragma unroll
+                for (int g = 0; g < kMaxGroup; ++g) pw[sp][g] = s[g];
+            }
         }
 #pragma unroll
-        for (int u = 0; u < D / 8; ++u) ((uint4 *)vs)[tid + u * D] = vreg[u];
+        for (int u = 0; u < KV; ++u) ((uint4 *)vs)[tid + u * T] = vreg[u];
         __syncthreads();
         // running max and sum per head; scores become weights
-        for (int g = warp; g < G; g += D / 32) {
+        for (int g = warp; g < G; g += T / 32) {
             float sv[D / 32], tmax = -INFINITY;
 #pragma unroll
             for (int i = 0; i < D / 32; ++i) {
@@ -354,13 +372,14 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
             }
         }
         __syncthreads();
-        // weighted sum of V from shared memory: thread = channel
+        // weighted sum of V from shared memory: thread = (channel, group of positions)
         {
 #pragma unroll
             for (int g = 0; g < kMaxGroup; ++g) acc[g] *= alpha[g];
+            const int tb = pg * (D / S), te = min(ntile, tb + D / S);
 #pragma unroll 8
-            for (int t = 0; t < ntile; ++t) {
-                const float v = __half2float(vs[t * D + tid]);
+            for (int t = tb; t < te; ++t) {
+                const float v = __half2float(vs[t * D + ch]);
                 const float4 pa = *(const float4 *)&pw[t][0], pb = *(const float4 *)&pw[t][4];
                 acc[0] += pa.x * v; acc[1] += pa.y * v; acc[2] += pa.z * v; acc[3] += pa.w * v;
                 acc[4] += pb.x * v; acc[5] += pb.y * v; acc[6] += pb.z * v; acc[7] += pb.w * v;
@@ -368,14 +387,30 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
         }
         __syncthreads();
     }
-
-    // publish this split
+    // the S groups' sums of a channel meet in shared memory (the V tile is free now)
+    if (S > 1) {
+        float *part_acc = (float *)vs;           // [S - 1][kMaxGroup][D]
+        if (pg > 0) {
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; ++g) part_acc[((pg - 1) * kMaxGroup + g) * D + ch] = acc[g];
+        }
+        __syncthreads();
+        if (pg == 0) {
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; ++g)
+#pragma unroll
+                for (int o = 0; o < S - 1; ++o) acc[g] += part_acc[(o * kMaxGroup + g) * D + ch];
+        }
+    }
+    // publish this split (threads of the first group: one per channel)
     float *mine = a.partial + ((size_t)hk * nsplit + split) * G * (D + 2);
-    for (int g = 0; g < G; ++g) {
-        mine[(size_t)g * (D + 2) + tid] = acc[g];
-        if (tid == 0) {
-            mine[(size_t)g * (D + 2) + D] = m_run[g];
-            mine[(size_t)g * (D + 2) + D + 1] = l_run[g];
+    if (tid < D) {
+        for (int g = 0; g < G; ++g) {
+            mine[(size_t)g * (D + 2) + tid] = acc[g];
+            if (tid == 0) {
+                mine[(size_t)g * (D + 2) + D] = m_run[g];
+                mine[(size_t)g * (D + 2) + D + 1] = l_run[g];
+            }
         }
     }
     __threadfence();
@@ -392,7 +427,7 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
     const float *base = a.partial + (size_t)hk * nsplit * G * (D + 2);
     float *wsm = &pw[0][0];                  // [G][kMaxSplits] weights (the tile buffer is free now)
     float *lsm = &qs[0][0];                  // [G][kMaxSplits] sums
-    for (int i = tid; i < nsplit * G; i += D) {
+    for (int i = tid; i < nsplit * G; i += T) {
         const int s = i / G, g = i - s * G;
         const float *p = base + ((size_t)s * G + g) * (D + 2);
         wsm[g * kMaxSplits + s] = __ldcg(p + D);
@@ -410,12 +445,13 @@ __global__ void __launch_bounds__(D) attention_decode_kernel(const AttnArgs a) {
         l_run[tid] = L;
     }
     __syncthreads();
-    for (int g = 0; g < G; ++g) {
+    // thread = (channel, head phase): the heads are dealt out over the S groups
+    for (int g = pg; g < G; g += S) {
         float o = 0.f;
-#pragma unroll 8
+#pragma unroll 16
         for (int s = 0; s < nsplit; ++s)
-            o += __ldcg(base + ((size_t)s * G + g) * (D + 2) + tid) * wsm[g * kMaxSplits + s];
-        a.out[(size_t)(hk * G + g) * D + tid] = __float2half_rn(o / l_run[g]);
+            o += __ldcg(base + ((size_t)s * G + g) * (D + 2) + ch) * wsm[g * kMaxSplits + s];
+        a.out[(size_t)(hk * G + g) * D + ch] = __float2half_rn(o / l_run[g]);
     }
     if (tid == 0) a.counters[hk] = 0u;
 }
@@ -484,13 +520,14 @@ size_t hlq_attention_workspace_bytes(int head_q, int head_kv, int dhead, int max
 
 int hlq_rope_cache_attention(const void *d_q, const void *d_k, const void *d_v, void *d_kcache, void *d_vcache,
                              const int *d_position, int head_q, int head_kv, int dhead, int max_ctx,
-                             float rotary_base, float scale, void *d_out, void *d_workspace,
+                             int kv_layout, float rotary_base, float scale, void *d_out, void *d_workspace,
                              size_t workspace_bytes, void *stream) {
     if (!d_q || !d_k || !d_v || !d_kcache || !d_vcache || !d_position || !d_out || !d_workspace)
         return HLQ_ERR_INVALID_ARGUMENT;
     if (head_q <= 0 || head_kv <= 0 || max_ctx <= 0 || head_q % head_kv) return HLQ_ERR_SHAPE;
     if (head_q / head_kv > kMaxGroup) return HLQ_ERR_UNSUPPORTED;
     if (dhead != 128 && dhead != 64) return HLQ_ERR_UNSUPPORTED;
+    if (kv_layout != HLQ_KV_POSITION_MAJOR && kv_layout != HLQ_KV_HEAD_MAJOR) return HLQ_ERR_INVALID_ARGUMENT;
     if (((uintptr_t)d_kcache | (uintptr_t)d_vcache | (uintptr_t)d_workspace) & 15) return HLQ_ERR_ALIGNMENT;
     const size_t need = hlq_attention_workspace_bytes(head_q, head_kv, dhead, max_ctx);
     if (workspace_bytes < need) return HLQ_ERR_WORKSPACE;
@@ -511,11 +548,14 @@ int hlq_rope_cache_attention(const void *d_q, const void *d_k, const void *d_v, 
     a.head_kv = head_kv;
     a.group = head_q / head_kv;
     a.max_ctx = max_ctx;
+    a.pos_stride = kv_layout == HLQ_KV_HEAD_MAJOR ? dhead : (long long)head_kv * dhead;
+    a.head_stride = kv_layout == HLQ_KV_HEAD_MAJOR ? (long long)max_ctx * dhead : dhead;
     a.rotary_base = rotary_base;
     a.scale = scale;
     if (dhead == 128)
-        return launch_glue(attention_decode_kernel<128>, dim3(head_kv, splits), dim3(128), 0, (cudaStream_t)stream, a);
-    return launch_glue(attention_decode_kernel<64>, dim3(head_kv, splits), dim3(64), 0, (cudaStream_t)stream, a);
+        return launch_glue(attention_decode_kernel<128, 4>, dim3(head_kv, splits), dim3(512), 0, (cudaStream_t)stream,
+                           a);
+    return launch_glue(attention_decode_kernel<64, 4>, dim3(head_kv, splits), dim3(256), 0, (cudaStream_t)stream, a);
 }
 
 }  // extern "C"

@@ -60,7 +60,8 @@ class TPDecoder:
 
     def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
                  group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False,
-                 fused_glue: bool = True, quantized_lm_head: bool = True, fused_inputs: bool = False):
+                 fused_glue: bool = True, quantized_lm_head: bool = True, fused_inputs: bool = False,
+                 kv_head_major: bool = True):
         if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
         self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
@@ -97,6 +98,11 @@ class TPDecoder:
             vfull = torch.randn((c.ctx, c.n_kv, c.head_dim), device=device, generator=gen).to(dt)
             L["kc"] = kfull[:, rank * self.hkv:(rank + 1) * self.hkv].contiguous()
             L["vc"] = vfull[:, rank * self.hkv:(rank + 1) * self.hkv].contiguous()
+            if kv_head_major:
+                # [head][position][dhead]: a head's positions are contiguous (a CTA of the attention
+                # kernel reads 32 KB runs instead of 256 bytes out of every 2 KB)
+                L["kc"] = L["kc"].permute(1, 0, 2).contiguous()
+                L["vc"] = L["vc"].permute(1, 0, 2).contiguous()
             del kfull, vfull
             # buffers
             L["xn"] = torch.empty((1, c.hidden), dtype=dt, device=device)
@@ -144,11 +150,13 @@ class TPDecoder:
         self.position = torch.tensor([pos], dtype=torch.int32, device=device)
         self.token = torch.zeros(1, dtype=torch.int64, device=device)    # input token id (a graph input)
         self.fused_glue = fused_glue
+        self.kv_head_major = kv_head_major
         self.next_index = torch.zeros(1, dtype=torch.int32, device=device)
         self.next_value = torch.zeros(1, dtype=torch.float32, device=device)
         if fused_glue:
             from .glue import DecodeAttention
-            self.attn = DecodeAttention(self.hq, self.hkv, c.head_dim, c.ctx, c.rope_theta, device)
+            self.attn = DecodeAttention(self.hq, self.hkv, c.head_dim, c.ctx, c.rope_theta, device,
+                                        head_major=kv_head_major)
         self.x = torch.empty((1, c.hidden), dtype=dt, device=device)
         self.xfinal = torch.empty((1, c.hidden), dtype=dt, device=device)
         # norms and SiLU folded into the table build of the linear that follows them
@@ -329,12 +337,12 @@ class TPDecoder:
             L["xn"].copy_(norm(x, L["ln1"]))
             self._groups_or_linears(L, "qkv", stream)
             q = self._rope(L["q_o"], self.hq)
-            L["kc"][self.pos] = self._rope(L["k_o"], self.hkv)
-            L["vc"][self.pos] = L["v_o"].view(self.hkv, c.head_dim)
-            att = F.scaled_dot_product_attention(q.view(1, self.hq, 1, c.head_dim).float(),
-                                                 L["kc"][:self.pos + 1].permute(1, 0, 2).unsqueeze(0).float(),
-                                                 L["vc"][:self.pos + 1].permute(1, 0, 2).unsqueeze(0).float(),
-                                                 enable_gqa=True)
+            self.kv_rows(L, "kc", self.pos, self.pos + 1)[0] = self._rope(L["k_o"], self.hkv)
+            self.kv_rows(L, "vc", self.pos, self.pos + 1)[0] = L["v_o"].view(self.hkv, c.head_dim)
+            att = F.scaled_dot_product_attention(
+                q.view(1, self.hq, 1, c.head_dim).float(),
+                self.kv_rows(L, "kc", 0, self.pos + 1).permute(1, 0, 2).unsqueeze(0).float(),
+                self.kv_rows(L, "vc", 0, self.pos + 1).permute(1, 0, 2).unsqueeze(0).float(), enable_gqa=True)
             L["att"].copy_(att.reshape(1, -1))
             self._row_parallel(L["o"], L["att"], L["o_o"])
             x.add_(L["o_o"])
@@ -401,6 +409,10 @@ class TPDecoder:
             per_layer += 4                                  # two norms, attention, gated silu
         tail = 1 if self.fused_inputs else (2 if self.fused_glue else 0)      # (final norm,) argmax
         return len(self.layers) * per_layer + tail + (1 if self.lm_w is not None else 0)
+
+    def kv_rows(self, L, name, lo, hi):
+        """Positions lo..hi-1 of a layer's K or V cache as a [position][head][dhead] view."""
+        return L[name][:, lo:hi].permute(1, 0, 2) if self.kv_head_major else L[name][lo:hi]
 
     def hidden_after_step(self):
         return self.xfinal if self.fused_inputs else self.x

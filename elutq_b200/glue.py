@@ -67,12 +67,14 @@ class DecodeAttention:
     """RoPE, KV-cache append and single-token attention as one kernel
     (launch_llama_qkv_apply_rotary + arm_cache + arm_attention for one token).
 
-    Caches are [max_ctx][head_kv][dhead] fp16 as in the reference; `position` is an int32
-    device tensor of one element (the index the new token is written at)."""
+    Caches are [max_ctx][head_kv][dhead] fp16 as in the reference, or with `head_major`
+    [head_kv][max_ctx][dhead] (faster: a head's positions are contiguous); `position` is an
+    int32 device tensor of one element (the index the new token is written at)."""
 
     def __init__(self, head_q: int, head_kv: int, dhead: int, max_ctx: int, rotary_base: float, device,
-                 scale: float | None = None):
+                 scale: float | None = None, head_major: bool = False):
         self.head_q, self.head_kv, self.dhead, self.max_ctx = head_q, head_kv, dhead, max_ctx
+        self.head_major = bool(head_major)     # caches [head_kv][max_ctx][dhead] instead of the reference's
         self.base = float(rotary_base)
         self.scale = float(scale) if scale is not None else float(dhead) ** -0.5
         need = _lib.lib().hlq_attention_workspace_bytes(head_q, head_kv, dhead, max_ctx)
@@ -86,13 +88,15 @@ class DecodeAttention:
             _f16(t, name)
         if position.dtype != torch.int32 or not position.is_cuda:
             raise ValueError("position must be an int32 CUDA tensor")
-        if tuple(kcache.shape) != (self.max_ctx, self.head_kv, self.dhead) or kcache.shape != vcache.shape:
-            raise ValueError("caches must be [max_ctx][head_kv][dhead]")
+        want = (self.head_kv, self.max_ctx, self.dhead) if self.head_major else (self.max_ctx, self.head_kv, self.dhead)
+        if tuple(kcache.shape) != want or kcache.shape != vcache.shape:
+            raise ValueError(f"caches must have shape {want}")
         if out is None:
             out = torch.empty((self.head_q, self.dhead), dtype=torch.float16, device=q.device)
         st = _lib.lib().hlq_rope_cache_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), kcache.data_ptr(),
                                                  vcache.data_ptr(), position.data_ptr(), self.head_q, self.head_kv,
-                                                 self.dhead, self.max_ctx, self.base, self.scale, out.data_ptr(),
+                                                 self.dhead, self.max_ctx, int(self.head_major), self.base, self.scale,
+                                                 out.data_ptr(),
                                                  self.ws.data_ptr(), self.nbytes, _stream(q))
         _lib.check(st, "hlq_rope_cache_attention")
         return out

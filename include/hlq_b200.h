@@ -320,7 +320,7 @@ int hlq_argmax(int n, const void *d_values, int dtype, int *d_index_out, float *
 /* One decode step of attention for one token, in one kernel:
  *   RoPE on q [head_q][dhead] and k [head_kv][dhead] with pairs (j, j + dhead/2) and angle
  *   position * rotary_base^(-2j/dhead)      (launch_llama_qkv_apply_rotary, arm_rotary.cpp:4-88),
- *   append of the roped k and of v at `position` into the caches [max_ctx][head_kv][dhead]
+ *   append of the roped k and of v at `position` into the caches (layout: hlq_kv_layout)
  *                                           (arm_cache, arm_cache.cpp:3-22),
  *   softmax(scale * q.K) V over positions 0..position with head h reading kv head
  *   h * head_kv / head_q                    (arm_attention, arm_attention.cpp:196-270, 320-340).
@@ -329,11 +329,16 @@ int hlq_argmax(int n, const void *d_values, int dtype, int *d_index_out, float *
  * and reported through the workspace status word (hlq_workspace_status).  dhead 64 or 128,
  * head_q / head_kv <= 8.  The workspace needs hlq_attention_workspace_bytes(...) bytes, zeroed
  * once with hlq_workspace_init; one workspace per stream. */
+typedef enum hlq_kv_layout {
+    HLQ_KV_POSITION_MAJOR = 0, /* [max_ctx][head_kv][dhead], the reference's caches (arm_cache.cpp:17-21)  */
+    HLQ_KV_HEAD_MAJOR = 1      /* [head_kv][max_ctx][dhead]: a head's positions are contiguous, which is    */
+                               /* what a GPU wants (a CTA reads 32 KB runs instead of 256 B every 2 KB)   */
+} hlq_kv_layout;
 size_t hlq_attention_workspace_bytes(int head_q, int head_kv, int dhead, int max_ctx);
 int hlq_rope_cache_attention(const void *d_q, const void *d_k, const void *d_v, void *d_kcache,
                              void *d_vcache, const int *d_position, int head_q, int head_kv,
-                             int dhead, int max_ctx, float rotary_base, float scale, void *d_out,
-                             void *d_workspace, size_t workspace_bytes, void *stream);
+                             int dhead, int max_ctx, int kv_layout, float rotary_base, float scale,
+                             void *d_out, void *d_workspace, size_t workspace_bytes, void *stream);
 
 /* ---- diagnostics -------------------------------------------------------------------- */
 

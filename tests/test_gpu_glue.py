@@ -104,8 +104,9 @@ ATT_CASES = [
 ]
 
 
+@pytest.mark.parametrize("head_major", [False, True])
 @pytest.mark.parametrize("hq,hkv,d,ctx,pos", ATT_CASES)
-def test_rope_cache_attention(hq, hkv, d, ctx, pos):
+def test_rope_cache_attention(hq, hkv, d, ctx, pos, head_major):
     rng = np.random.default_rng(hq * 7 + hkv * 3 + d + pos)
     base = 500000.0
     q = rng.standard_normal((hq, d)).astype(np.float16)
@@ -118,8 +119,11 @@ def test_rope_cache_attention(hq, hkv, d, ctx, pos):
     GO.cache_append(kc_ref, vc_ref, GO.rope(k, pos, base), v, pos)
     ref = GO.attention_single(GO.rope(q, pos, base), kc_ref, vc_ref, pos + 1, d ** -0.5)
 
-    att = glue.DecodeAttention(hq, hkv, d, ctx, base, DEV)
-    dkc, dvc = t16(kc), t16(vc)
+    att = glue.DecodeAttention(hq, hkv, d, ctx, base, DEV, head_major=head_major)
+    # the reference's caches are [position][head][dhead]; head-major keeps a head's positions together
+    lay = (lambda c: np.ascontiguousarray(c.transpose(1, 0, 2))) if head_major else (lambda c: c)
+    unlay = (lambda c: c.transpose(1, 0, 2)) if head_major else (lambda c: c)
+    dkc, dvc = t16(lay(kc)), t16(lay(vc))
     position = torch.tensor([pos], dtype=torch.int32, device=DEV)
     out = att.forward(t16(q), t16(k), t16(v), dkc, dvc, position)
     torch.cuda.synchronize()
@@ -129,7 +133,7 @@ def test_rope_cache_attention(hq, hkv, d, ctx, pos):
     assert err <= 1e-3, err
     # the cache: v copied bit-exactly, roped k within an fp16 ulp (fp32 sin/cos of a large
     # angle against float64), everything else untouched
-    gk, gv = dkc.cpu().numpy(), dvc.cpu().numpy()
+    gk, gv = unlay(dkc.cpu().numpy()), unlay(dvc.cpu().numpy())
     assert np.array_equal(gv.view(np.uint16), vc_ref.view(np.uint16))
     close16(gk[pos], kc_ref[pos], rtol=4e-3, atol=2e-3)
     mask = np.ones(ctx, dtype=bool)
