@@ -256,11 +256,19 @@ __global__ void __launch_bounds__(D *S) attention_decode_kernel(const AttnArgs a
         const float ang = (float)pos * powf(a.rotary_base, -(float)(2 * tid) / (float)D);
         float sn, cs;
         sincosf(ang, &sn, &cs);
-        for (int g = 0; g < G; ++g) {
-            const __half *qp = a.q + (size_t)(hk * G + g) * D;
-            const float q1 = __half2float(qp[tid]), q2 = __half2float(qp[tid + D / 2]);
-            qs[g][tid] = __half2float(__float2half_rn(q1 * cs - q2 * sn)) * a.scale;
-            qs[g][tid + D / 2] = __half2float(__float2half_rn(q1 * sn + q2 * cs)) * a.scale;
+        float q1[kMaxGroup], q2[kMaxGroup];        // all loads first: they do not wait for one another
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g) {
+            const __half *qp = a.q + (size_t)(hk * G + (g < G ? g : 0)) * D;
+            q1[g] = __half2float(qp[tid]);
+            q2[g] = __half2float(qp[tid + D / 2]);
+        }
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g) {
+            if (g < G) {
+                qs[g][tid] = __half2float(__float2half_rn(q1[g] * cs - q2[g] * sn)) * a.scale;
+                qs[g][tid + D / 2] = __half2float(__float2half_rn(q1[g] * sn + q2[g] * cs)) * a.scale;
+            }
         }
         if (pos >= t0 && pos < t1) {             // this CTA's share holds the new position: append
             const __half *kp = a.k + (size_t)hk * D;
@@ -294,9 +302,11 @@ __global__ void __launch_bounds__(D *S) attention_decode_kernel(const AttnArgs a
         // part of a K row and its share of the V tile (both coalesced).
         uint4 kreg[KV], vreg[KV];
         if (sp < ntile) {
-            const uint4 *kr = (const uint4 *)(a.kcache + (size_t)(tile + sp) * row_stride + head_off) + part * KV;
+            // the S threads of a position take every S-th 16-byte chunk of the row: their loads
+            // coalesce, and their reads of the queries below fall into different banks
+            const uint4 *kr = (const uint4 *)(a.kcache + (size_t)(tile + sp) * row_stride + head_off) + part;
 #pragma unroll
-            for (int c = 0; c < KV; ++c) kreg[c] = kr[c];
+            for (int c = 0; c < KV; ++c) kreg[c] = kr[c * S];
         }
 #pragma unroll
         for (int u = 0; u < KV; ++u) {
@@ -321,7 +331,7 @@ __global__ void __launch_bounds__(D *S) attention_decode_kernel(const AttnArgs a
                         kf[2 * e] = f.x;
                         kf[2 * e + 1] = f.y;
                     }
-                    const int c0 = 8 * (part * KV + c);
+                    const int c0 = 8 * (c * S + part);
 #pragma unroll
                     for (int g = 0; g < kMaxGroup; ++g) {
                         if (g < G) {
@@ -422,36 +432,42 @@ __global__ void __launch_bounds__(D *S) attention_decode_kernel(const AttnArgs a
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // merge of the splits: all (max, sum) pairs first, in parallel, then per head the
-    // weights exp(max_s - max) in shared memory, then every thread sums its channel
+    // merge of the splits: thread = (channel, head phase), the heads are dealt out over the S
+    // groups.  A thread loads its channel's partial sums and the (max, sum) pairs of all splits
+    // at once (one round trip), forms the weights exp(max_s - max) itself and writes fp16.
     const float *base = a.partial + (size_t)hk * nsplit * G * (D + 2);
-    float *wsm = &pw[0][0];                  // [G][kMaxSplits] weights (the tile buffer is free now)
-    float *lsm = &qs[0][0];                  // [G][kMaxSplits] sums
-    for (int i = tid; i < nsplit * G; i += T) {
-        const int s = i / G, g = i - s * G;
-        const float *p = base + ((size_t)s * G + g) * (D + 2);
-        wsm[g * kMaxSplits + s] = __ldcg(p + D);
-        lsm[g * kMaxSplits + s] = __ldcg(p + D + 1);
-    }
-    __syncthreads();
-    if (tid < G) {
-        float M = -INFINITY, L = 0.f;
-        for (int s = 0; s < nsplit; ++s) M = fmaxf(M, wsm[tid * kMaxSplits + s]);
-        for (int s = 0; s < nsplit; ++s) {
-            const float w = expf(wsm[tid * kMaxSplits + s] - M);
-            wsm[tid * kMaxSplits + s] = w;
-            L += lsm[tid * kMaxSplits + s] * w;
-        }
-        l_run[tid] = L;
-    }
-    __syncthreads();
-    // thread = (channel, head phase): the heads are dealt out over the S groups
     for (int g = pg; g < G; g += S) {
-        float o = 0.f;
-#pragma unroll 16
-        for (int s = 0; s < nsplit; ++s)
-            o += __ldcg(base + ((size_t)s * G + g) * (D + 2) + ch) * wsm[g * kMaxSplits + s];
-        a.out[(size_t)(hk * G + g) * D + ch] = __float2half_rn(o / l_run[g]);
+        float M = -INFINITY;
+        for (int s0 = 0; s0 < nsplit; s0 += 16) {
+            float ov[16], mv[16], lv[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int s = min(s0 + u, nsplit - 1);
+                const float *p = base + ((size_t)s * G + g) * (D + 2);
+                ov[u] = __ldcg(p + ch);
+                mv[u] = __ldcg(p + D);
+                lv[u] = s0 + u < nsplit ? __ldcg(p + D + 1) : 0.f;
+            }
+            float Mc = M;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) Mc = fmaxf(Mc, mv[u]);
+            // running rescale across chunks of 16 splits (one chunk for caches up to 2048 positions)
+            const float r = s0 ? expf(M - Mc) : 0.f;
+            if (s0 == 0) {
+                acc[0] = 0.f;
+                acc[1] = 0.f;
+            }
+            acc[0] *= r;
+            acc[1] *= r;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const float w = s0 + u < nsplit ? expf(mv[u] - Mc) : 0.f;
+                acc[0] += ov[u] * w;          // weighted output of this channel
+                acc[1] += lv[u] * w;          // weighted sum of the softmax denominators
+            }
+            M = Mc;
+        }
+        a.out[(size_t)(hk * G + g) * D + ch] = __float2half_rn(acc[0] / acc[1]);
     }
     if (tid == 0) a.counters[hk] = 0u;
 }
