@@ -24,15 +24,6 @@ int note_cuda(cudaError_t e) {
 }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-static bool is_device_pointer(const void *p) {
-    cudaPointerAttributes attr;
-    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return false;
-    }
-    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
-}
-
 static int check_shape(int n, int k, int g, int q) {
     if (n <= 0 || k <= 0 || g <= 0) return HLQ_ERR_INVALID_ARGUMENT;
     if (q < 1 || q > 4 || k % g || k % 8 || g % 8) return HLQ_ERR_SHAPE;
