@@ -61,7 +61,7 @@ class TPDecoder:
     def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
                  group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False,
                  fused_glue: bool = True, quantized_lm_head: bool = True, fused_inputs: bool = False,
-                 kv_head_major: bool = True):
+                 kv_head_major: bool = True, export=None):
         if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
         self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
@@ -73,9 +73,14 @@ class TPDecoder:
         self.layers = []
         self.linear_bytes = 0
 
-        def load(n, k, mode, lseed, bits=c.bits, groupsize=c.groupsize):
-            gen.manual_seed(lseed)          # every rank draws the full tensor and keeps its shard
-            lin = _random_export(n, k, bits, groupsize, gen, device)
+        def load(n, k, mode, lseed, bits=c.bits, groupsize=c.groupsize, given=None):
+            if given is not None:           # a linear of an exported model (host arrays)
+                if given.out_channel != n or given.in_channel != k:
+                    raise ValueError(f"exported linear is {given.out_channel}x{given.in_channel}, expected {n}x{k}")
+                lin = given
+            else:
+                gen.manual_seed(lseed)      # every rank draws the full tensor and keeps its shard
+                lin = _random_export(n, k, bits, groupsize, gen, device)
             w = HLQWeight.from_export(lin, device=device.index, tp_rank=rank, tp_size=world, shard_mode=mode)
             self.linear_bytes += w.info.algorithmic_bytes
             return w
@@ -83,21 +88,33 @@ class TPDecoder:
         dt = torch.float16
         for li in range(c.layers):
             s0 = seed + li * 16
+            ex = export.layers[li] if export is not None else None
+            giv = (lambda name: ex.linears[name]) if ex is not None else (lambda name: None)
             L = {
-                "q": load(q_dim, c.hidden, rows, s0 + 0), "k": load(kv_dim, c.hidden, rows, s0 + 1),
-                "v": load(kv_dim, c.hidden, rows, s0 + 2), "o": load(c.hidden, q_dim, cols, s0 + 3),
-                "gate": load(c.ffn, c.hidden, rows, s0 + 4), "up": load(c.ffn, c.hidden, rows, s0 + 5),
-                "down": load(c.hidden, c.ffn, cols, s0 + 6),
+                "q": load(q_dim, c.hidden, rows, s0 + 0, given=giv("q")),
+                "k": load(kv_dim, c.hidden, rows, s0 + 1, given=giv("k")),
+                "v": load(kv_dim, c.hidden, rows, s0 + 2, given=giv("v")),
+                "o": load(c.hidden, q_dim, cols, s0 + 3, given=giv("o")),
+                "gate": load(c.ffn, c.hidden, rows, s0 + 4, given=giv("gate")),
+                "up": load(c.ffn, c.hidden, rows, s0 + 5, given=giv("up")),
+                "down": load(c.hidden, c.ffn, cols, s0 + 6, given=giv("down")),
             }
             gen.manual_seed(s0 + 7)
-            L["ln1"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
-            L["ln2"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
+            if ex is not None:
+                L["ln1"] = torch.from_numpy(ex.ln1.astype("float16")).to(device)
+                L["ln2"] = torch.from_numpy(ex.ln2.astype("float16")).to(device)
+            else:
+                L["ln1"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
+                L["ln2"] = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
             # this rank's KV heads of a random cache filled up to ctx-1, [position][head][dhead]
             # as the reference keeps it (arm_cache.cpp:17-21)
             kfull = torch.randn((c.ctx, c.n_kv, c.head_dim), device=device, generator=gen).to(dt)
             vfull = torch.randn((c.ctx, c.n_kv, c.head_dim), device=device, generator=gen).to(dt)
             L["kc"] = kfull[:, rank * self.hkv:(rank + 1) * self.hkv].contiguous()
             L["vc"] = vfull[:, rank * self.hkv:(rank + 1) * self.hkv].contiguous()
+            if export is not None:          # a real model starts with an empty cache
+                L["kc"].zero_()
+                L["vc"].zero_()
             if kv_head_major:
                 # [head][position][dhead]: a head's positions are contiguous (a CTA of the attention
                 # kernel reads 32 KB runs instead of 256 bytes out of every 2 KB)
@@ -123,11 +140,25 @@ class TPDecoder:
                 L["gu"] = HLQGroup([L["gate"], L["up"]], max_m=1)
             self.layers.append(L)
         gen.manual_seed(seed + 100003)
-        self.embed = (torch.randn((c.vocab, c.hidden), device=device, generator=gen) * 0.5).to(dt)
-        self.norm = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
         vs = c.vocab // world
         self.lm_head = self.lm_w = None
-        if quantized_lm_head:
+        if export is not None:
+            from .format import ExportedLinear as _EL
+            self.embed = torch.from_numpy(export.embed.astype("float16")).to(device)
+            self.norm = torch.from_numpy(export.final_norm.astype("float16")).to(device)
+            quantized_lm_head = isinstance(export.lm_head, _EL)
+            if quantized_lm_head:
+                self.lm_w = load(c.vocab, c.hidden, rows, 0, given=export.lm_head)
+                self.logits = torch.empty((1, vs), dtype=dt, device=device)
+            else:
+                self.lm_head = torch.from_numpy(
+                    export.lm_head[rank * vs:(rank + 1) * vs].astype("float16")).to(device).contiguous()
+        else:
+            self.embed = (torch.randn((c.vocab, c.hidden), device=device, generator=gen) * 0.5).to(dt)
+            self.norm = (1 + 0.1 * torch.randn(c.hidden, device=device, generator=gen)).to(dt)
+        if export is not None:
+            pass                            # loaded above
+        elif quantized_lm_head:
             # the reference quantizes lm_head to w4g128 whatever the body uses (HLQ.py:76-78)
             self.lm_w = load(c.vocab, c.hidden, rows, seed + 100007, bits=4, groupsize=128)
             self.logits = torch.empty((1, vs), dtype=dt, device=device)
@@ -197,6 +228,24 @@ class TPDecoder:
         if fused_allreduce and world > 1:
             from .tp import FusedAllReduceComm
             self.comm = FusedAllReduceComm(max_n=c.hidden, max_m=1, device=device.index, group=group)
+
+    @classmethod
+    def from_export(cls, export, n_heads: int, n_kv: int, device, head_dim: int = None, ctx: int = 2048,
+                    rope_theta: float = 500000.0, rank: int = 0, world: int = 1, group=None, **kw):
+        """A decoder over an exported model (`model_io.read_model_export(dir)` or the path of
+        the directory): what `llama::load_model` does (llama.cpp:59-115), with the linears
+        sharded over the tensor-parallel ranks.  Head counts are not part of the export."""
+        if isinstance(export, (str, bytes)):
+            from .model_io import read_model_export
+            export = read_model_export(export)
+        q_lin = export.layers[0].linears["q"]
+        if head_dim is None:
+            head_dim = q_lin.out_channel // n_heads
+        if q_lin.out_channel != n_heads * head_dim or export.layers[0].linears["k"].out_channel != n_kv * head_dim:
+            raise ValueError("head counts do not match the exported q/k projections")
+        cfg = DecoderConfig(export.hidden, export.ffn, len(export.layers), n_heads, n_kv, head_dim, export.vocab,
+                            bits=q_lin.bits, groupsize=q_lin.groupsize, ctx=ctx, rope_theta=rope_theta)
+        return cls(cfg, device, rank, world, group=group, export=export, **kw)
 
     # ------------------------------------------------------------------------------------
     def _linear(self, w, x, out):
