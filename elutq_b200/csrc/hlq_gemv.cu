@@ -466,7 +466,10 @@ __device__ __forceinline__ void compute_tile(const Tile<Q, GPW> &t, const uint32
 // the restart of the load ring): CTAs that get many short slices would otherwise finish last.
 // Only launches of several jobs need it (a single job's slices are all alike); there
 // GemvArgs::seg_cost = kSegCost, else 0.
-constexpr int kSegCost = 28;
+#ifndef HLQ_SEG_COST
+#define HLQ_SEG_COST 40
+#endif
+constexpr int kSegCost = HLQ_SEG_COST;
 __host__ __device__ static inline long long launch_units(int slices, int duos, int seg_cost) {
     return (long long)slices * (duos + seg_cost);
 }
