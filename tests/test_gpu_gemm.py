@@ -51,9 +51,17 @@ def test_gemm_matches_oracle(built_lib, q, n, k, g, m, bias):
     assert mod.workspace.kernel_status() == 0
     assert O.normwise_error(y32.cpu().numpy(), ref) <= TOL
     assert O.normwise_error(y16.float().cpu().numpy(), ref) <= TOL
-    # automatic dispatch takes the same kernel for more than 16 rows
+    # automatic dispatch: fp32 outputs go to this kernel above 16 rows, 16-bit outputs above 32
+    # (below that two rows share every lookup of the LUT kernel, which is then faster)
     ya = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32)
     assert torch.equal(ya, y32)
+    ya16 = lm.linear_forward(x, mod.weight, mod.workspace)
+    if m > 32:
+        assert torch.equal(ya16, y16)
+    else:
+        lut = lm.linear_forward(x, mod.weight, mod.workspace, impl=_lib.IMPL_LUT8)
+        assert O.normwise_error(ya16.float().cpu().numpy(), lut.float().cpu().numpy()) <= 1e-6
+        assert O.normwise_error(ya16.float().cpu().numpy(), ref) <= TOL
 
 
 def test_prefill_shape_of_the_13b_configuration(built_lib):
