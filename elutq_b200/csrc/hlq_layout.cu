@@ -34,6 +34,39 @@ __global__ void unpack_bits_kernel(const uint8_t *__restrict__ packed, uint8_t *
     }
 }
 
+// Nearest-combination quantizer of the reference (GPTQ/quant.py:154-174): per element the
+// argmin over the 2^q values sum_j s_j * c_j of |value - (w - z)|, first minimum on ties;
+// combination c has bit j = (c >> (q - 1 - j)) & 1 (first column slowest, quant.py:12-16).
+template <int Q>
+__global__ void quantize_with_scales_kernel(const float *__restrict__ w, const float *__restrict__ scales,
+                                            const float *__restrict__ zeros, uint8_t *__restrict__ out,
+                                            int64_t total, int g) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t b = i / g;
+        float s[Q];
+#pragma unroll
+        for (int j = 0; j < Q; ++j) s[j] = scales[b * Q + j];
+        const float t = w[i] - zeros[b];
+        float best = INFINITY;
+        int arg = 0;
+#pragma unroll
+        for (int c = 0; c < (1 << Q); ++c) {
+            float v = 0.f;
+#pragma unroll
+            for (int j = 0; j < Q; ++j)
+                if ((c >> (Q - 1 - j)) & 1) v = __fadd_rn(v, s[j]);
+            const float dist = fabsf(__fsub_rn(v, t));
+            if (dist < best) {
+                best = dist;
+                arg = c;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < Q; ++j) out[i * Q + j] = (uint8_t)((arg >> (Q - 1 - j)) & 1);
+    }
+}
+
 // one thread per 16-byte lane word of a cell
 __global__ void repack_planes_kernel(const uint8_t *__restrict__ w_quant, uint8_t *__restrict__ planes,
                                      StreamDims d) {
@@ -145,6 +178,25 @@ static int grid_for(int64_t items, int threads) {
 using namespace hlq;
 
 extern "C" {
+
+int hlq_quantize_with_scales_device(const float *d_w, const float *d_scales, const float *d_zeros, uint8_t *d_out,
+                                    int64_t blocks, int g, int q, void *stream) {
+    if (blocks < 0 || g <= 0) return HLQ_ERR_INVALID_ARGUMENT;
+    if (q < 1 || q > 4) return HLQ_ERR_SHAPE;
+    const int64_t total = blocks * g;
+    if (total == 0) return HLQ_OK;
+    if (!d_w || !d_scales || !d_zeros || !d_out) return HLQ_ERR_INVALID_ARGUMENT;
+    const dim3 grid = grid_for(total, 256);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (q) {
+        case 1: quantize_with_scales_kernel<1><<<grid, 256, 0, st>>>(d_w, d_scales, d_zeros, d_out, total, g); break;
+        case 2: quantize_with_scales_kernel<2><<<grid, 256, 0, st>>>(d_w, d_scales, d_zeros, d_out, total, g); break;
+        case 3: quantize_with_scales_kernel<3><<<grid, 256, 0, st>>>(d_w, d_scales, d_zeros, d_out, total, g); break;
+        default: quantize_with_scales_kernel<4><<<grid, 256, 0, st>>>(d_w, d_scales, d_zeros, d_out, total, g); break;
+    }
+    count_launch();
+    return note_cuda(cudaGetLastError());
+}
 
 int hlq_pack_bits_device(const uint8_t *d_bits, uint8_t *d_packed, int q, int64_t n, int64_t k,
                          void *stream) {

@@ -208,3 +208,29 @@ def unrepack_host(planes: np.ndarray, meta: np.ndarray, n: int, k: int, g: int, 
     _lib.check(L.hlq_unrepack_host(_ptr(planes), _ptr(meta), n, k, g, q, _ptr(wq), _ptr(ws), _ptr(wz)),
                "hlq_unrepack_host")
     return ExportedLinear(wq, ws.view(np.float16), wz.view(np.float16), None, g)
+
+
+def quantize_with_scales_device(w, scales, zeros):
+    """Assignment step of the reference's quantizer (quant.py:154-174) on the GPU.
+
+    ``w`` fp32 CUDA ``[blocks, g]``, ``scales`` fp32 ``[blocks, q]``, ``zeros`` fp32 ``[blocks]``
+    -> uint8 CUDA ``[blocks, g, q]`` of 0/1 (what ``HLQ.export`` receives as ``quantized_w``
+    after its reshape, HLQ.py:207-208)."""
+    import torch
+    from . import _lib
+    if not (w.is_cuda and scales.is_cuda and zeros.is_cuda):
+        raise RuntimeError("quantize_with_scales_device runs on CUDA tensors only")
+    w = w.contiguous().float()
+    scales = scales.contiguous().float()
+    zeros = zeros.contiguous().float().reshape(-1)
+    blocks, g = w.shape
+    q = scales.shape[1]
+    if scales.shape[0] != blocks or zeros.numel() != blocks:
+        raise ValueError("one row of scales and one zero per block")
+    out = torch.empty((blocks, g, q), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        st = _lib.lib().hlq_quantize_with_scales_device(w.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                                        out.data_ptr(), blocks, g, q,
+                                                        torch.cuda.current_stream(w.device).cuda_stream)
+    _lib.check(st, "hlq_quantize_with_scales_device")
+    return out

@@ -78,6 +78,16 @@ typedef struct hlq_weight_info {
     int64_t algorithmic_bytes; /* q*n*k/8 + 2*(q+1)*n*k/g: planes + fp16 scales + fp16 zeros */
 } hlq_weight_info;
 
+/* ---- quantizer step ----------------------------------------------------------------- */
+
+/* Assignment step of the reference's quantizer on the device: for every element of
+ * w [blocks][g] (fp32) the nearest of the 2^q values sum_j scales[b][j] * c_j to w - zeros[b],
+ * first minimum on ties; out is uint8 [blocks][g][q] of 0/1 (column j pairs with scale j).
+ * Replaces: quantize_with_scales, GPTQ/quant.py:154-174.  (The fit of scales and zeros,
+ * quant.py:104-153, is not part of this library.) */
+int hlq_quantize_with_scales_device(const float *d_w, const float *d_scales, const float *d_zeros,
+                                    uint8_t *d_out, int64_t blocks, int g, int q, void *stream);
+
 /* ---- bit-plane packing -------------------------------------------------------------- */
 
 /* bits: uint8 [q][n][k] of 0/1  ->  packed: uint8 [q][n][k/8]; channel 8i+j goes to bit j
