@@ -72,6 +72,11 @@ SIGNATURES = {
     "hlq_tp_comm_handle": (c_int, [c_void_p, c_void_p]),
     "hlq_tp_comm_connect": (c_int, [c_void_p, c_void_p]),
     "hlq_tp_comm_free": (c_int, [c_void_p]),
+    "hlq_tp_comm_buffer_bytes": (c_int, [c_void_p, POINTER(c_size_t)]),
+    "hlq_tp_comm_local_buffer": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "hlq_tp_comm_connect_pointers": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "hlq_tp_comm_set_spin_limit": (c_int, [c_void_p, c_int]),
+    "hlq_static_scratch_status": (c_int, [c_int, c_void_p, POINTER(c_int)]),
     "hlq_linear_forward_allreduce": (c_int, [c_int] * 3 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t,
                                              c_void_p, c_void_p, c_void_p]),
     "hlq_group_create": (c_int, [POINTER(c_void_p), c_int, POINTER(c_void_p), c_int]),

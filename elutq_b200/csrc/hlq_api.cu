@@ -87,6 +87,10 @@ static int alloc_buffers(hlq_weight *w, bool with_bias) {
     HLQ_CUDA(cudaMalloc((void **)&w->d_planes, (size_t)w->planes_bytes));
     HLQ_CUDA(cudaMalloc((void **)&w->d_meta, (size_t)w->meta_bytes));
     if (with_bias) HLQ_CUDA(cudaMalloc((void **)&w->d_bias, (size_t)w->n * 2));
+    if (w->layout == HLQ_LAYOUT_EXPORT) {
+        HLQ_CUDA(cudaMalloc((void **)&w->d_status, kWsHeader));
+        HLQ_CUDA(cudaMemset(w->d_status, 0, kWsHeader));
+    }
     return HLQ_OK;
 }
 
@@ -94,6 +98,8 @@ static void free_buffers(hlq_weight *w) {
     if (w->d_planes) cudaFree(w->d_planes);
     if (w->d_meta) cudaFree(w->d_meta);
     if (w->d_bias) cudaFree(w->d_bias);
+    if (w->d_status) cudaFree(w->d_status);
+    w->d_status = nullptr;
     w->d_planes = nullptr;
     w->d_meta = nullptr;
     w->d_bias = nullptr;
@@ -366,7 +372,7 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
     }
     switch (impl) {
         case 1: return launch_lut8_gemv(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream);
-        case 2: return launch_lut4_gemv(w, m, d_x, x_dtype, d_y, y_dtype, stream);
+        case 2: return launch_lut4_gemv(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream);
         case 3: return launch_dequant_gemm(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream);
         default: return HLQ_ERR_INVALID_ARGUMENT;
     }

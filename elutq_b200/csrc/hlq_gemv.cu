@@ -41,8 +41,10 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <vector>
 
@@ -57,7 +59,7 @@ constexpr int kFinalizers = kFinalWarps * 32;
 constexpr int kThreads = kConsumers + kFinalizers;
 constexpr uint32_t kTableBytes = 65536;
 constexpr uint32_t kAuxBytes = 8192;
-constexpr int kSpinLimit = 1 << 22;
+constexpr int kDefaultSpinLimit = 1 << 22;   // polls of one bounded wait unless the caller sets another
 
 // named barriers (0 is __syncthreads)
 constexpr int kBarConsumers = 1;   // 512 consumer threads
@@ -91,7 +93,7 @@ struct Job {
 // memory.  recv[p] is rank p's receive buffer as mapped into this
 // process; slot (parity, source rank, row of x, output row or block).
 struct TpDev {
-    uint2 *recv[8];       // slots of {fp32 bits, launch number}: value and flag travel in one 8-byte store
+    unsigned long long *recv[8];   // slots of (launch number << 32 | fp32 bits): value and flag are one 64-bit word
     unsigned *seq;        // number of finished fused launches on this rank
     unsigned *done;       // blocks summed so far in the current launch
     int rank, world, max_m, np_cap;
@@ -108,6 +110,7 @@ struct GemvArgs {
     int row_base;         // first row of x this launch serves (grid.y passes of R rows follow)
     int y_is_f32;         // host only: fp32 outputs keep one row per pass (fp32 table entries)
     int one_row_passes;   // host only: a job has an input transform (one row of x per pass)
+    int spin_limit;       // polls after which a bounded wait gives up
     Job single;
 };
 
@@ -210,15 +213,18 @@ __device__ __forceinline__ float ldcg_f32(const float *p) {
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
     return v;
 }
-// traffic of the fused all-reduce: one aligned 8-byte store carries a value and the launch
-// number that validates it, so neither side needs a fence (a system-scope fence or release
-// per block costs 5-15 us while the accumulators' reductions are in flight)
-__device__ __forceinline__ void st_relaxed_sys_v2(uint2 *p, uint32_t a, uint32_t b) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+// traffic of the fused all-reduce: ONE naturally aligned 64-bit scalar carries a value (low
+// word) and the launch number that validates it (high word).  A 64-bit scalar access is
+// single-copy atomic, so a reader sees both halves of one store or neither, and neither side
+// needs a fence (a system-scope fence or release per block costs 5-15 us while the
+// accumulators' reductions are in flight)
+__device__ __forceinline__ void st_relaxed_sys_b64(unsigned long long *p, uint32_t value, uint32_t tag) {
+    const unsigned long long v = ((unsigned long long)tag << 32) | value;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2 *p) {
-    uint2 v;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_b64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ float x_to_float(uint16_t bits, int dtype) {
@@ -256,10 +262,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// false when the wait gave up
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
-    for (int i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(mbar, parity)) return true;
+// false when the wait gave up.  `fail` is the CTA-wide failure flag in shared memory: the
+// wait that runs out sets it, and once it is set every later wait of the CTA tries once and
+// gives up, so that a kernel whose peer or copy never arrives drains in microseconds instead
+// of spinning its full limit again at every wait.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity, volatile int *fail, int limit) {
+    if (mbar_try_wait(mbar, parity)) return true;
+    if (!*fail) {
+        for (int i = 0; i < limit; ++i) {
+            if (mbar_try_wait(mbar, parity)) return true;
+            if ((i & 255) == 255 && *fail) break;
+        }
+    }
+    *fail = 1;
     return false;
 }
 __device__ __forceinline__ void tma_bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
@@ -574,7 +589,8 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
     }
     unsigned char *aux = smem_raw + (aux_u32 - sbase);
     float *xsum = (float *)(aux + (R == 2 ? kAuxXsum2 : kAuxXsum));    // [row][16]
-    int *fail = (int *)(aux + kAuxFlag);
+    volatile int *fail = (volatile int *)(aux + kAuxFlag);
+    const int spin = a.spin_limit;
     Seg *ring = (Seg *)(aux + kAuxSeg);
     const uint32_t mb_desc = aux_u32 + kAuxMbarDesc, mb_x = aux_u32 + kAuxMbarX;
 
@@ -669,9 +685,9 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         }
         for (int i = 0;; ++i) {
             const int slot = i & 1;
-            if (!mbar_wait_bounded(mb_desc + 8 * slot, (i >> 1) & 1)) *fail = 1;
+            const bool have = mbar_wait_bounded(mb_desc + 8 * slot, (i >> 1) & 1, fail, spin);
             const Seg sg = ring[slot];
-            if (!sg.live) break;
+            if (!have || !sg.live) break;     // no descriptor: nothing may be read from the ring slot
             last_sg = sg;
             named_bar_sync_dyn(kBarSegDone + slot, kThreads);      // consumers are done with it
             named_bar_sync<kBarFinalizers, kFinalizers>();         // every finalizer holds its copy
@@ -733,7 +749,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                                 const long long slot_row =
                                     (((long long)par * tp->world + tp->rank) * tp->max_m + sg.mrow) * tp->np_cap + rows[b];
                                 for (int p = 0; p < tp->world; ++p)
-                                    st_relaxed_sys_v2(tp->recv[p] + slot_row, __float_as_uint(o), epoch);
+                                    st_relaxed_sys_b64(tp->recv[p] + slot_row, __float_as_uint(o), epoch);
                             }
                             if (lane == 0) sg.counters[rows[b] / kBlockRows] = 0;
                         }
@@ -754,12 +770,17 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
                 float sum = 0.f;
                 bool ok = true;
                 for (int src = 0; src < tp->world; ++src) {
-                    const uint2 *slot = tp->recv[tp->rank] +
-                                        (((long long)par * tp->world + src) * tp->max_m + sg.mrow) * tp->np_cap + row;
-                    uint2 v = ld_relaxed_sys_v2(slot);
-                    for (int it = 0; it < kSpinLimit && v.y != epoch; ++it) v = ld_relaxed_sys_v2(slot);
-                    ok = ok && (v.y == epoch);
-                    sum += __uint_as_float(v.x);
+                    const unsigned long long *slot =
+                        tp->recv[tp->rank] + (((long long)par * tp->world + src) * tp->max_m + sg.mrow) * tp->np_cap + row;
+                    unsigned long long v = ld_relaxed_sys_b64(slot);
+                    // a peer that never arrives: the first wait that runs out ends all later ones
+                    const int lim = *fail ? 0 : spin;
+                    for (int it = 0; it < lim && (uint32_t)(v >> 32) != epoch; ++it) {
+                        v = ld_relaxed_sys_b64(slot);
+                        if ((it & 255) == 255 && *fail) break;
+                    }
+                    ok = ok && ((uint32_t)(v >> 32) == epoch);
+                    sum += __uint_as_float((uint32_t)v);
                 }
                 if (!ok) *fail = 1;
                 if (row < sg.n) store_y(sg.y, sg.y_base + row, sum, sg.y_dtype);
@@ -821,10 +842,10 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
             load_tile<Q, GPW>(t1, pl + kConsumerWarps * kDuoPlaneBytes, mp + kConsumerWarps * kDuoMetaElems);
     };
 
-    if (!mbar_wait_bounded(mb_desc, 0)) *fail = 1;
     {
+        const bool have = mbar_wait_bounded(mb_desc, 0, fail, spin);
         const Seg sg = ring[0];
-        if (!sg.live) return;
+        if (!have || !sg.live) return;
         open_segment(sg);
     }
     for (int i = 0;; ++i) {
@@ -861,7 +882,7 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
             rms_job = cur_job;
             named_bar_sync<kBarConsumers, kConsumers>();     // red[] may be rewritten by the next job
         }
-        if (!mbar_wait_bounded(mb_x + 8 * slot, (i >> 1) & 1)) *fail = 1;
+        mbar_wait_bounded(mb_x + 8 * slot, (i >> 1) & 1, fail, spin);
         const uint16_t *xs = (const uint16_t *)(aux + kX) + slot * (R * kSliceK);
         // group sums (warps 0..R-1) and the 64 tables of 256 subset sums (all consumer warps)
         const uint16_t *xs2 = (const uint16_t *)(aux + kAuxX2) + slot * kSliceK;     // input transform only
@@ -997,11 +1018,12 @@ __global__ void __launch_bounds__(kThreads, 1) lut8_gemv_kernel(const __grid_con
         }
 
         // first loads of the next segment, then hand this one to the finalizers
-        if (!mbar_wait_bounded(mb_desc + 8 * (slot ^ 1), ((i + 1) >> 1) & 1)) *fail = 1;
+        const bool have = mbar_wait_bounded(mb_desc + 8 * (slot ^ 1), ((i + 1) >> 1) & 1, fail, spin);
         const Seg nx = ring[slot ^ 1];
-        if (nx.live) open_segment(nx);
+        const bool more = have && nx.live;
+        if (more) open_segment(nx);
         named_bar_arrive_dyn(kBarSegDone + slot, kThreads);
-        if (!nx.live) break;
+        if (!more) break;
     }
 }
 
@@ -1060,9 +1082,8 @@ __global__ void __launch_bounds__(kGenThreads) lut4_gemv_kernel(const GenArgs a)
                          (uint32_t)valid * 2u, mbar);
         }
         for (int i = valid + tid; i < kGenTileK; i += kGenThreads) xs[i] = 0;
-        const bool ok = mbar_wait_bounded(mbar, phase);
+        mbar_wait_bounded(mbar, phase, (volatile int *)&fail, kDefaultSpinLimit);
         phase ^= 1u;
-        if (!ok) fail = 1;
         __syncthreads();
         if (fail) {
             if (tid == 0) atomicExch(a.status, 1);
@@ -1192,21 +1213,25 @@ Workspace carve_workspace(void *base, int m, const StreamDims &d) {
 struct DeviceInfo {
     int sms = 0;
     int max_dyn_smem = 0;
-    bool ok = false;
+    std::atomic<bool> ok{false};
 };
 static DeviceInfo g_dev[64];
+static std::mutex g_first_use;     // serializes the per-device lookups done on first use
 
 static int device_info(int device, DeviceInfo **out) {
     if (device < 0 || device >= 64) return HLQ_ERR_INVALID_ARGUMENT;
     DeviceInfo &d = g_dev[device];
-    if (!d.ok) {
-        int major = 0;
-        HLQ_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
-        if (major != 10) return HLQ_ERR_NO_DEVICE;
-        HLQ_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, device));
-        HLQ_CUDA(cudaDeviceGetAttribute(&d.max_dyn_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin,
-                                        device));
-        d.ok = true;
+    if (!d.ok.load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_first_use);
+        if (!d.ok.load(std::memory_order_relaxed)) {
+            int major = 0;
+            HLQ_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+            if (major != 10) return HLQ_ERR_NO_DEVICE;
+            HLQ_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, device));
+            HLQ_CUDA(cudaDeviceGetAttribute(&d.max_dyn_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                            device));
+            d.ok.store(true, std::memory_order_release);
+        }
     }
     *out = &d;
     return HLQ_OK;
@@ -1236,14 +1261,15 @@ constexpr uint32_t kLut8DynSmem = 65536 - 1024 + kTableBytes + kAuxBytes;
 
 template <int Q, int GPW, int R, bool XOP>
 static int launch_lut8_inst(const GemvArgs &args, dim3 grid, cudaStream_t stream) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     HLQ_CUDA(cudaGetDevice(&dev));
     auto kernel = lut8_gemv_kernel<Q, GPW, R, XOP>;
-    if (!configured[dev & 63]) {
+    if (!configured[dev & 63].load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_first_use);
         HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)kLut8DynSmem));
-        configured[dev & 63] = true;
+        configured[dev & 63].store(true, std::memory_order_release);
     }
     return launch_pdl(kernel, grid, dim3(kThreads), kLut8DynSmem, stream, args);
 }
@@ -1349,6 +1375,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         a.total_units = launch_units(d.slices, d.duos, 0);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
+        a.spin_limit = kDefaultSpinLimit;
         a.y_is_f32 = y_dtype == HLQ_F32;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
@@ -1370,24 +1397,25 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
 // and a latency-critical section cannot afford the device-wide synchronization cudaMalloc and
 // cudaFree imply.  For them the LUT GEMV can keep its scratch (status word, completion
 // counters, fp32 row accumulators) in the array below instead of a caller-provided workspace.
-// Every GPU that loads this library holds the array until the process exits.
+// Every GPU that loads this library holds the array until the process exits.  The first 256
+// bytes hold the kernels' status word; the calls never clear it (hlq_static_scratch_status
+// reads and clears it), so a failure stays visible until somebody has looked.
 constexpr size_t kStaticScratchBytes = 1u << 20;   // 1 MiB, must match HLQ_STATIC_SCRATCH_BYTES
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address.
 // The address is looked up once per device, with that device current.
 static int static_scratch_address(int device, void **out) {
-    static void *addr[64] = {};
-    static bool have[64] = {};
+    static std::atomic<void *> addr[64];
     if (device < 0 || device >= 64) return HLQ_ERR_INVALID_ARGUMENT;
-    if (!have[device]) {
-        void *p = nullptr;
+    void *p = addr[device].load(std::memory_order_acquire);
+    if (!p) {
+        std::lock_guard<std::mutex> lock(g_first_use);
         HLQ_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
         if (!p) return HLQ_ERR_CUDA;
-        addr[device] = p;
-        have[device] = true;
+        addr[device].store(p, std::memory_order_release);
     }
-    *out = addr[device];
+    *out = p;
     return HLQ_OK;
 }
 
@@ -1412,7 +1440,9 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         const int mc = (m - m0) < kLutMaxM ? (m - m0) : kLutMaxM;
         // The array keeps whatever the previous call left; counters and accumulators must
         // start at zero, so clear the part this launch uses (a memset node, no allocation).
-        HLQ_CUDA(cudaMemsetAsync(scratch, 0, lut_scratch_bytes(mc, d), stream));
+        // The header with the status word is left alone: see hlq_static_scratch_status.
+        HLQ_CUDA(cudaMemsetAsync((unsigned char *)scratch + kWsHeader, 0, lut_scratch_bytes(mc, d) - kWsHeader,
+                                 stream));
         const Workspace ws = carve_workspace(scratch, mc, d);
         GemvArgs a = {};
         a.jobs = nullptr;
@@ -1420,6 +1450,7 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         a.total_units = launch_units(d.slices, d.duos, 0);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
+        a.spin_limit = kDefaultSpinLimit;
         a.y_is_f32 = y_dtype == HLQ_F32;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
@@ -1446,6 +1477,20 @@ extern "C" int hlq_linear_forward_static(int m, int k, int n, const void *d_x, i
     return hlq::launch_lut8_gemv_static(w, m, d_x, x_dtype, d_y, y_dtype, (cudaStream_t)stream);
 }
 
+extern "C" int hlq_static_scratch_status(int device, void *stream, int *kernel_status) {
+    if (!kernel_status) return HLQ_ERR_INVALID_ARGUMENT;
+    int cur = -1;
+    HLQ_CUDA(cudaGetDevice(&cur));
+    if (cur != device) return HLQ_ERR_INVALID_ARGUMENT;       // the device must be current
+    void *scratch = nullptr;
+    const int rc = hlq::static_scratch_address(device, &scratch);
+    if (rc) return rc;
+    HLQ_CUDA(cudaMemcpyAsync(kernel_status, scratch, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    HLQ_CUDA(cudaMemsetAsync(scratch, 0, sizeof(int), (cudaStream_t)stream));    // read once, then clear
+    HLQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return *kernel_status ? HLQ_ERR_KERNEL : HLQ_OK;
+}
+
 // ---- fused all-reduce for row-parallel linears ----------------------------------------------
 struct hlq_tp_comm {
     int device = 0, rank = 0, world = 1, max_m = 1, np_cap = 0;
@@ -1454,7 +1499,19 @@ struct hlq_tp_comm {
     void *peer[8] = {};                  // every rank's buffer as mapped here
     hlq::TpDev *d_tp = nullptr;
     bool connected = false;
+    bool ipc = false;                    // peer[] came from cudaIpcOpenMemHandle
+    int spin_limit = hlq::kDefaultSpinLimit;
 };
+
+// Fills the device-side descriptor once every rank's buffer address is known.
+static int tp_comm_publish(hlq_tp_comm *c) {
+    hlq::TpDev t = {};
+    for (int p = 0; p < c->world; ++p) t.recv[p] = (unsigned long long *)c->peer[p];
+    t.seq = (unsigned *)(c->local + c->seq_off);
+    t.done = t.seq + 1;
+    t.rank = c->rank; t.world = c->world; t.max_m = c->max_m; t.np_cap = c->np_cap;
+    return hlq::note_cuda(cudaMemcpy(c->d_tp, &t, sizeof(t), cudaMemcpyHostToDevice));
+}
 
 extern "C" {
 
@@ -1467,7 +1524,7 @@ int hlq_tp_comm_create(hlq_tp_comm **out, int rank, int world, int max_n, int ma
     if (!c) return HLQ_ERR_INVALID_ARGUMENT;
     c->device = device; c->rank = rank; c->world = world; c->max_m = max_m;
     c->np_cap = (max_n + hlq::kBlockRows - 1) / hlq::kBlockRows * hlq::kBlockRows;
-    const size_t recv = (size_t)2 * world * max_m * c->np_cap * sizeof(uint2);
+    const size_t recv = (size_t)2 * world * max_m * c->np_cap * sizeof(unsigned long long);
     c->seq_off = (recv + 255) / 256 * 256;
     c->bytes = c->seq_off + 256;
     int prev = -1;
@@ -1514,19 +1571,51 @@ int hlq_tp_comm_connect(hlq_tp_comm *c, const void *handles) {
         memcpy(&h, (const char *)handles + 64 * p, 64);
         rc = hlq::note_cuda(cudaIpcOpenMemHandle(&c->peer[p], h, cudaIpcMemLazyEnablePeerAccess));
     }
+    if (!rc) rc = tp_comm_publish(c);
+    if (prev >= 0) cudaSetDevice(prev);
     if (!rc) {
-        hlq::TpDev t = {};
-        for (int p = 0; p < c->world; ++p) {
-            t.recv[p] = (uint2 *)c->peer[p];
-        }
-        t.seq = (unsigned *)(c->local + c->seq_off);
-        t.done = t.seq + 1;
-        t.rank = c->rank; t.world = c->world; t.max_m = c->max_m; t.np_cap = c->np_cap;
-        rc = hlq::note_cuda(cudaMemcpy(c->d_tp, &t, sizeof(t), cudaMemcpyHostToDevice));
+        c->connected = true;
+        c->ipc = true;
     }
+    return rc;
+}
+
+int hlq_tp_comm_buffer_bytes(const hlq_tp_comm *c, size_t *bytes) {
+    if (!c || !bytes) return HLQ_ERR_INVALID_ARGUMENT;
+    *bytes = c->bytes;
+    return HLQ_OK;
+}
+
+int hlq_tp_comm_connect_pointers(hlq_tp_comm *c, void *const *d_peer_buffers) {
+    if (!c || (!d_peer_buffers && c->world > 1)) return HLQ_ERR_INVALID_ARGUMENT;
+    if (c->connected) return HLQ_ERR_INVALID_ARGUMENT;
+    for (int p = 0; p < c->world; ++p) {
+        if (p == c->rank) {
+            c->peer[p] = c->local;
+            continue;
+        }
+        if (!d_peer_buffers[p] || ((uintptr_t)d_peer_buffers[p] & 255)) return HLQ_ERR_ALIGNMENT;
+        c->peer[p] = d_peer_buffers[p];
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (cudaSetDevice(c->device) != cudaSuccess) return HLQ_ERR_NO_DEVICE;
+    const int rc = tp_comm_publish(c);
     if (prev >= 0) cudaSetDevice(prev);
     if (!rc) c->connected = true;
     return rc;
+}
+
+int hlq_tp_comm_local_buffer(const hlq_tp_comm *c, void **d_buffer) {
+    if (!c || !d_buffer) return HLQ_ERR_INVALID_ARGUMENT;
+    *d_buffer = c->local;
+    return HLQ_OK;
+}
+
+int hlq_tp_comm_set_spin_limit(hlq_tp_comm *c, int polls) {
+    if (!c || polls < 1) return HLQ_ERR_INVALID_ARGUMENT;
+    c->spin_limit = polls;
+    return HLQ_OK;
 }
 
 int hlq_tp_comm_free(hlq_tp_comm *c) {
@@ -1535,7 +1624,7 @@ int hlq_tp_comm_free(hlq_tp_comm *c) {
     cudaGetDevice(&prev);
     cudaSetDevice(c->device);
     for (int p = 0; p < c->world; ++p)
-        if (p != c->rank && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
+        if (c->ipc && p != c->rank && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
     if (c->local) cudaFree(c->local);
     if (c->d_tp) cudaFree(c->d_tp);
     if (prev >= 0) cudaSetDevice(prev);
@@ -1578,6 +1667,7 @@ int hlq_linear_forward_allreduce_op(int m, int k, int n, const void *d_x, int x_
     a.total_units = launch_units(d.slices, d.duos, 0);
     a.status = ws.status;
     a.dyn_smem = kLut8DynSmem;
+    a.spin_limit = comm->spin_limit;
     fill_job(a.single, w, d, d_x, x_dtype, d_y, y_dtype, ws.partial, ws.counters, 0);
     rc = apply_input_op(a.single, op, x_dtype, 0);
     if (rc) return rc;
@@ -1726,6 +1816,7 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.seg_cost = g->seg_cost;
     a.status = (int *)g->d_scratch;
     a.dyn_smem = kLut8DynSmem;
+    a.spin_limit = kDefaultSpinLimit;
     a.y_is_f32 = g->jobs_host[0].y_dtype == HLQ_F32;
     a.one_row_passes = g->one_row_passes;
     int ctas = force_ctas > 0 ? force_ctas : di->sms;
@@ -1770,20 +1861,10 @@ int hlq_group_free(hlq_group *g) {
 
 namespace hlq {
 
-// Status word used by the generic kernel when the caller gave no workspace.
-static int *generic_status_word(int device) {
-    static int *words[64] = {};
-    if (!words[device & 63]) {
-        int *p = nullptr;
-        if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
-        cudaMemset(p, 0, 256);
-        words[device & 63] = p;
-    }
-    return words[device & 63];
-}
-
+// The kernel's status word is the caller's workspace header when there is one (so that
+// hlq_workspace_status sees it, as for the other kernels), else the word the handle owns.
 int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
-                     cudaStream_t stream) {
+                     void *workspace, size_t workspace_bytes, cudaStream_t stream) {
     if (w->layout != HLQ_LAYOUT_EXPORT) return HLQ_ERR_UNSUPPORTED;
     if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return HLQ_ERR_ALIGNMENT;
@@ -1797,8 +1878,8 @@ int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
     a.bias = w->d_bias;
     a.x = x;
     a.y = y;
-    a.status = generic_status_word(w->device);
-    if (!a.status) return note_cuda(cudaErrorMemoryAllocation);
+    a.status = (workspace && workspace_bytes >= kWsHeader) ? (int *)workspace : w->d_status;
+    if (!a.status) return HLQ_ERR_WORKSPACE;
     a.n = w->n; a.k = w->k; a.g = w->g;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     int rows_per_cta = (w->n + 4 * di->sms - 1) / (4 * di->sms);

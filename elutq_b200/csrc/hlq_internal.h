@@ -19,6 +19,10 @@ struct hlq_weight {
     uint16_t *d_meta = nullptr;
     uint16_t *d_bias = nullptr;
     int64_t planes_bytes = 0, meta_bytes = 0;
+    // HLQ_LAYOUT_EXPORT only: 256 zeroed bytes whose first word is the generic kernel's status
+    // word when a forward call brings no workspace (allocated with the handle, never in a
+    // launch path).
+    int *d_status = nullptr;
 };
 
 namespace hlq {
@@ -50,7 +54,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
                      void *workspace, size_t workspace_bytes, cudaStream_t stream,
                      const hlq_input_op *op = nullptr);
 int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
-                     cudaStream_t stream);
+                     void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, void *y,
                         int y_dtype, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream);

@@ -313,6 +313,16 @@ class HLQLinear(torch.nn.Module):
         return cls.from_exported(lin, device=device, **kw)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        # a batch larger than the one the workspace was sized for: make a larger workspace
+        # (an allocation: not allowed while a CUDA graph is being captured)
+        m = x.numel() // self.in_features
+        need = workspace_bytes(m, self.in_features, self.out_features, self.bits, self.groupsize)
+        if need > self.workspace.nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"a batch of {m} rows needs a {need}-byte workspace; construct the module "
+                                   "with max_batch >= the batch before capturing a graph")
+            torch.cuda.current_stream(x.device).synchronize()
+            self.workspace = Workspace(need, self.weight.device)
         return linear_forward(x, self.weight, self.workspace, impl=self.impl)
 
     def extra_repr(self) -> str:

@@ -83,8 +83,7 @@ typedef struct hlq_weight_info {
 /* Assignment step of the reference's quantizer on the device: for every element of
  * w [blocks][g] (fp32) the nearest of the 2^q values sum_j scales[b][j] * c_j to w - zeros[b],
  * first minimum on ties; out is uint8 [blocks][g][q] of 0/1 (column j pairs with scale j).
- * Replaces: quantize_with_scales, GPTQ/quant.py:154-174.  (The fit of scales and zeros,
- * quant.py:104-153, is not part of this library.) */
+ * Replaces: quantize_with_scales, GPTQ/quant.py:154-174. */
 int hlq_quantize_with_scales_device(const float *d_w, const float *d_scales, const float *d_zeros,
                                     uint8_t *d_out, int64_t blocks, int g, int q, void *stream);
 
@@ -199,20 +198,27 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
  * cudaMalloc/cudaFree.  The scratch (status word, completion counters, fp32 accumulators)
  * lives in a fixed HLQ_STATIC_SCRATCH_BYTES array inside the library, which every GPU that
  * loads the library holds until the process exits.  The call allocates nothing.
- *  - Limit: problems whose hlq_workspace_bytes(m, k, n, bits, g) exceeds
- *    HLQ_STATIC_SCRATCH_BYTES are rejected with HLQ_ERR_WORKSPACE (m = 1: n up to ~250 000
- *    rows; m = 16: n up to ~16 000).  Weights in the exported layout: HLQ_ERR_UNSUPPORTED.
+ *  - Limit: the scratch of one launch, 256 + 128 * r * ceil(n/32) + 4 * r * 32 * ceil(n/32)
+ *    bytes with r = min(m, 16) rows per launch (counters rounded up to 256 bytes; more rows run
+ *    as several launches of 16), must fit HLQ_STATIC_SCRATCH_BYTES, else HLQ_ERR_WORKSPACE
+ *    (m = 1: n up to ~250 000 rows; m >= 16: n up to ~15 000).  Weights in the exported
+ *    layout: HLQ_ERR_UNSUPPORTED.
  *  - The first call on a device looks the array's address up (with the weight's device
  *    current, as for hlq_linear_forward); make that first call before any stream capture.
- *  - All calls on a device share the one array.  Each call clears the part it uses on
- *    `stream` before its kernel, so leftovers of earlier calls do not matter, but two calls
- *    whose work overlaps on the GPU (different streams) race on it: keep them on one stream
- *    or order them with events.
- * This entry point has no counterpart in the reference (its CPU operator gets its
+ *  - All calls on a device share the one array.  Each call clears the counters and
+ *    accumulators it uses on `stream` before its kernel, so leftovers of earlier calls do not
+ *    matter, but two calls whose work overlaps on the GPU (different streams) race on it:
+ *    keep them on one stream or order them with events.
+ *  - The kernels' status word is the first word of the array.  The forward calls never clear
+ *    it; hlq_static_scratch_status reads it (synchronizing `stream`), clears it, and returns
+ *    HLQ_ERR_KERNEL with a non-zero *kernel_status exactly as hlq_workspace_status does, so a
+ *    failure of any call since the last look is reported.  `device` must be current.
+ * These entry points have no counterpart in the reference (its CPU operator gets its
  * temp_workplace from the caller, arm_gemm.h:4-14). */
 #define HLQ_STATIC_SCRATCH_BYTES (1u << 20)
 int hlq_linear_forward_static(int m, int k, int n, const void *d_x, int x_dtype, void *d_y,
                               int y_dtype, const hlq_weight *w, void *stream);
+int hlq_static_scratch_status(int device, void *stream, int *kernel_status);
 
 /* ---- groups: many independent linears in one launch ----------------------------------- */
 
@@ -256,10 +262,24 @@ int hlq_tp_comm_create(hlq_tp_comm **out, int rank, int world, int max_n, int ma
 int hlq_tp_comm_handle(const hlq_tp_comm *c, void *handle64);
 /* handles: world x 64 bytes, in rank order (this rank's own entry is ignored). */
 int hlq_tp_comm_connect(hlq_tp_comm *c, const void *handles);
+/* The same connection for ranks that live in ONE process (one thread per GPU with peer access
+ * enabled, or a test that stands in for an absent peer with a buffer nobody writes):
+ * d_peer_buffers[p] is rank p's receive buffer (hlq_tp_comm_local_buffer of its communicator,
+ * or any zeroed, 256-byte aligned device allocation of hlq_tp_comm_buffer_bytes bytes) as
+ * addressable from this rank's device; this rank's own entry is ignored. */
+int hlq_tp_comm_buffer_bytes(const hlq_tp_comm *c, size_t *bytes);
+int hlq_tp_comm_local_buffer(const hlq_tp_comm *c, void **d_buffer);
+int hlq_tp_comm_connect_pointers(hlq_tp_comm *c, void *const *d_peer_buffers);
+/* Polls after which a wait for a peer gives up (default 2^22, a few seconds).  The first
+ * wait of a CTA that runs out makes all its later waits give up at once, the kernel ends
+ * within microseconds of that, and the workspace status word reads 1.  After such a failure
+ * the ranks' launch numbers no longer agree: free the communicator and create a new one. */
+int hlq_tp_comm_set_spin_limit(hlq_tp_comm *c, int polls);
 int hlq_tp_comm_free(hlq_tp_comm *c);
 /* As hlq_linear_forward for m <= max_m rows and a streaming-layout weight; y receives the sum
  * over all ranks.  A rank that never arrives makes the others give up after a bounded wait
- * and report through the workspace status word. */
+ * and report through the workspace status word (hlq_workspace_status returns HLQ_ERR_KERNEL
+ * with *kernel_status == 1). */
 int hlq_linear_forward_allreduce(int m, int k, int n, const void *d_x, int x_dtype, void *d_y,
                                  int y_dtype, void *d_workspace, size_t workspace_bytes,
                                  const hlq_weight *w, hlq_tp_comm *comm, void *stream);

@@ -154,6 +154,36 @@ def test_w3g128_batches_at_llama_shapes(L, n, k, m):
     assert O.normwise_error(run(mod, d["x"]), ref) <= TOL_F16
 
 
+@pytest.mark.parametrize("q", [2, 3])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_paired_rows_at_every_llama_shape(L, n, k, q):
+    """2, 4, 8 and 16 rows of activations (passes of two rows with fp16 table entries) at all
+    four projection shapes of the benchmark set, w2g128 and w3g128, the longest accumulation
+    (k = 14336) included."""
+    d = O.synth_linear(n, k, q, 128, m=16, seed=70 + q)
+    lin, mod = make(d, 128, max_batch=16)
+    ref = O.hlq_linear(d["x"].astype(np.float32), d["w_quant"], d["w_scale"], d["w_zero"], 128, dtype=np.float32)
+    for m in (2, 4, 8, 16):
+        assert O.normwise_error(run(mod, d["x"][:m]), ref[:m]) <= TOL_F16, m
+    assert O.normwise_error(run(mod, d["x"][:3], torch.float32), ref[:3]) <= 2e-5
+
+
+def test_linear_module_grows_its_workspace(L):
+    """A module built with the default max_batch takes a prefill-sized batch: the workspace is
+    re-made when a call needs more (fp16 and bf16 activations, tensor-core path)."""
+    d = O.synth_linear(256, 1024, 2, 64, m=64, seed=12)
+    lin, mod = make(d, 64)
+    ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], 64)
+    x = torch.from_numpy(d["x"]).cuda()
+    y = mod(x)
+    yb = mod(x.bfloat16())
+    torch.cuda.synchronize()
+    assert mod.workspace.kernel_status() == 0
+    assert O.normwise_error(y.float().cpu().numpy(), ref) <= TOL_F16
+    refb = O.hlq_linear(x.bfloat16().float().cpu().numpy(), d["w_quant"], d["w_scale"], d["w_zero"], 64)
+    assert O.normwise_error(yb.float().cpu().numpy(), refb) <= TOL_BF16
+
+
 def test_size_independent_properties(L):
     """Properties at full size: scaling x by two scales y by two, zero activations give
     exactly the bias, and the two independent kernels agree."""
