@@ -619,7 +619,8 @@ def run_decode(args):
     cfg = dataclasses.replace(cfg, bits=args.bits, groupsize=args.groupsize)
     fused = world > 1 and not args.nccl_allreduce
     dec = TPDecoder(cfg, dev, rank, world, seed=args.seed, grouped=not args.ungrouped,
-                    fused_allreduce=fused, fused_glue=not args.torch_glue)
+                    fused_allreduce=fused, fused_glue=not args.torch_glue,
+                    chain=not (args.launch_per_op or args.nccl_allreduce or args.torch_glue or args.ungrouped))
     parity = None
     if world > 1 and fused:
         parity = tp_parity(dec, dev, world)
@@ -663,10 +664,11 @@ def run_decode(args):
     sec = statistics.median(blocks) / 1e3 / args.steps
     sec_e2e = statistics.median([float(v) for v in t[len(ms):]]) / 1e3 / args.steps
     assert dec.ws.kernel_status() == 0 and (not dec.fused_glue or dec.attn.status() == 0)
+    assert dec.chain is None or dec.chain.status() == 0
     peaks = measured_peaks()
     my_bytes = float(dec.linear_bytes)
     launches = dec.launches_per_step()
-    gemv_launches = len(dec.layers) * (4 if dec.grouped else 7) + 1
+    gemv_launches = 2 if dec.use_chain else len(dec.layers) * (4 if dec.grouped else 7) + 1
     line = {
         "metric": "decode_tokens_per_s", "value": 1.0 / sec, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "repeats": REPEATS, "ms_per_step": sec * 1e3,
@@ -759,6 +761,8 @@ def main():
     ap.add_argument("--torch-glue", action="store_true", help="PyTorch ops between the linears")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="NCCL all-reduce after o and down instead of the one fused into the GEMV kernel")
+    ap.add_argument("--launch-per-op", action="store_true",
+                    help="one launch per op (8 per layer) instead of the decode chain (one persistent kernel)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host every step")
     ap.add_argument("--no-extras", action="store_true", help="N = 1: skip the gemv / batches / prefill objects")
     # projection set (gemv object and --workload gemv)

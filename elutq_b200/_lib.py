@@ -90,6 +90,15 @@ SIGNATURES = {
     "hlq_linear_forward_allreduce_op": (c_int, [c_int] * 3 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t,
                                                 c_void_p, c_void_p, c_void_p, c_void_p]),
     "hlq_group_bind_op": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p]),
+    "hlq_chain_create": (c_int, [POINTER(c_void_p), c_int, c_int]),
+    "hlq_chain_add_linears": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
+    "hlq_chain_add_attention": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_float, c_float, c_void_p, c_void_p, c_size_t]),
+    "hlq_chain_finish": (c_int, [c_void_p, c_void_p]),
+    "hlq_chain_forward": (c_int, [c_void_p, c_void_p]),
+    "hlq_chain_status": (c_int, [c_void_p, c_void_p, POINTER(c_int)]),
+    "hlq_chain_trace": (c_int, [c_void_p, c_void_p, c_int, POINTER(c_int)]),
+    "hlq_chain_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64)]),
+    "hlq_chain_free": (c_int, [c_void_p]),
     "hlq_rmsnorm": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "hlq_gated_silu": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "hlq_argmax": (c_int, [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
@@ -108,6 +117,14 @@ class InputOp(ctypes.Structure):
                 ("d_res_out", c_void_p)]
 
 
+class ChainLinear(ctypes.Structure):
+    """hlq_chain_linear: one linear of a decode-chain stage."""
+    _fields_ = [("w", c_void_p), ("d_x", c_void_p), ("d_y", c_void_p), ("in_kind", c_int), ("out_kind", c_int),
+                ("d_gamma", c_void_p), ("eps", c_float), ("norm_channels", c_int), ("ss_in", c_int), ("ss_out", c_int)]
+
+
+HLQ_CHAIN_IN_PLAIN, HLQ_CHAIN_IN_NORM, HLQ_CHAIN_IN_ATTENTION = 0, 1, 2
+HLQ_CHAIN_OUT_STORE, HLQ_CHAIN_OUT_RESIDUAL, HLQ_CHAIN_OUT_GATED_SILU = 0, 1, 2
 HLQ_INPUT_PLAIN, HLQ_INPUT_GATED_SILU, HLQ_INPUT_ADD_RMSNORM = 0, 1, 2
 HLQ_KV_POSITION_MAJOR, HLQ_KV_HEAD_MAJOR = 0, 1
 

@@ -17,6 +17,7 @@
 
 #include <stdint.h>
 
+#include "hlq_attn_dev.cuh"
 #include "hlq_internal.h"
 
 namespace hlq {
@@ -42,17 +43,6 @@ int launch_glue(KernelT kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t
     HLQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, args...));
     count_launch();
     return HLQ_OK;
-}
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int d = 16; d; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int d = 16; d; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
-    return v;
 }
 
 // ---- RMSNorm (+ residual add) -------------------------------------------------------------
@@ -199,278 +189,15 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T *v, int n, int *in
 }
 
 // ---- RoPE + cache append + single-token attention -----------------------------------------
-// Grid (head_kv, splits); D threads (one per channel of a head).  A CTA owns one kv head, its
-// G = head_q / head_kv query heads and a contiguous share of the positions 0..pos.  Per tile of
-// D positions: one thread per position forms the G scores (its K row against the roped,
-// pre-scaled queries in shared memory), the warps update the running max/sum per head and turn
-// scores into weights in shared memory, then one thread per channel adds weight * V.  Partial
-// (max, sum, unnormalized output) go to the workspace; the CTA that arrives last for its kv
-// head (a counter that it re-zeroes) merges the splits and writes fp16 output.
-constexpr int kMaxGroup = 8;
-constexpr int kMaxSplits = 64;      // kMaxGroup * kMaxSplits floats fit the tile buffers (D >= 64)
-
-struct AttnArgs {
-    const __half *q, *k, *v;      // this token's projections: [head_q][D], [head_kv][D], [head_kv][D]
-    __half *kcache, *vcache;      // [max_ctx][head_kv][D] or [head_kv][max_ctx][D]
-    long long pos_stride, head_stride;   // elements between two positions / two kv heads of a cache
-    const int *position;          // device: position of this token = number of cached tokens
-    __half *out;                  // [head_q][D]
-    float *partial;               // [head_kv][splits][G][D + 2]
-    unsigned *counters;           // [head_kv]
-    int *status;
-    int head_q, head_kv, group, max_ctx;
-    float rotary_base, scale;
-};
-
-// S threads share a position in the score phase (each takes D/S channels of the K row) and
-// S groups of threads share the positions of a tile in the weighted sum of V: with one warp
-// per scheduler the kernel was bound by the latency of its own instruction chains.
+// Grid (head_kv, splits), D * S threads: every CTA runs one unit of hlq_attn_dev.cuh.
 template <int D, int S>
 __global__ void __launch_bounds__(D *S) attention_decode_kernel(const AttnArgs a) {
-    constexpr int T = D * S;               // threads
-    constexpr int KV = D / 8 / S;          // 16-byte loads per thread for its part of a K row / of the V tile
-    static_assert(S == 1 || S == 2 || S == 4, "threads per position");
-    static_assert(KV >= 1 && (S - 1) * kMaxGroup * D * 4 <= D * D * 2, "the partial sums reuse the V tile");
-    __shared__ __align__(16) float qs[kMaxGroup][D];       // roped queries times scale
-    __shared__ __align__(16) float pw[D][kMaxGroup];       // scores, then weights, of a tile
-    __shared__ __align__(16) __half vs[D * D];             // the V tile: [position][channel]
-    __shared__ float alpha[kMaxGroup], m_run[kMaxGroup], l_run[kMaxGroup];
-    __shared__ int is_last;
+    __shared__ AttnSmem<D> sm;
     pdl_enter();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int hk = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
-    const int G = a.group;
-    int pos = *a.position;
-    if (pos < 0 || pos >= a.max_ctx) {           // refuse to write outside the cache
-        if (tid == 0) atomicExch(a.status, 3);
-        pos = pos < 0 ? 0 : a.max_ctx - 1;
-    }
-    const int nkv = pos + 1;
-    const int per = (nkv + nsplit - 1) / nsplit;
-    const int t0 = split * per, t1 = min(nkv, t0 + per);
-    const size_t row_stride = (size_t)a.pos_stride;
-    const size_t head_off = (size_t)hk * (size_t)a.head_stride;
-
-    // RoPE: pair (j, j + D/2), angle = pos * base^(-2j/D), results rounded to fp16 as stored
-    if (tid < D / 2) {
-        const float ang = (float)pos * powf(a.rotary_base, -(float)(2 * tid) / (float)D);
-        float sn, cs;
-        sincosf(ang, &sn, &cs);
-        float q1[kMaxGroup], q2[kMaxGroup];        // all loads first: they do not wait for one another
-#pragma unroll
-        for (int g = 0; g < kMaxGroup; ++g) {
-            const __half *qp = a.q + (size_t)(hk * G + (g < G ? g : 0)) * D;
-            q1[g] = __half2float(qp[tid]);
-            q2[g] = __half2float(qp[tid + D / 2]);
-        }
-#pragma unroll
-        for (int g = 0; g < kMaxGroup; ++g) {
-            if (g < G) {
-                qs[g][tid] = __half2float(__float2half_rn(q1[g] * cs - q2[g] * sn)) * a.scale;
-                qs[g][tid + D / 2] = __half2float(__float2half_rn(q1[g] * sn + q2[g] * cs)) * a.scale;
-            }
-        }
-        if (pos >= t0 && pos < t1) {             // this CTA's share holds the new position: append
-            const __half *kp = a.k + (size_t)hk * D;
-            const float k1 = __half2float(kp[tid]), k2 = __half2float(kp[tid + D / 2]);
-            __half *kc = a.kcache + (size_t)pos * row_stride + head_off;
-            kc[tid] = __float2half_rn(k1 * cs - k2 * sn);
-            kc[tid + D / 2] = __float2half_rn(k1 * sn + k2 * cs);
-        }
-    } else if (tid < D && pos >= t0 && pos < t1) {
-        const int j = tid - D / 2;
-        __half *vc = a.vcache + (size_t)pos * row_stride + head_off;
-        const __half *vp = a.v + (size_t)hk * D;
-        vc[j] = vp[j];
-        vc[j + D / 2] = vp[j + D / 2];
-    }
-    if (tid < kMaxGroup) {
-        m_run[tid] = -INFINITY;
-        l_run[tid] = 0.f;
-        alpha[tid] = 0.f;
-    }
-    float acc[kMaxGroup];
-#pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g) acc[g] = 0.f;
-    __syncthreads();
-
-    const int sp = tid / S, part = tid % S;      // score phase: position of the tile, part of its row
-    const int ch = tid % D, pg = tid / D;        // V phase: channel, group of positions
-    for (int tile = t0; tile < t1; tile += D) {
-        const int ntile = min(D, t1 - tile);
-        // All global loads of the tile are issued before anything is computed: this thread's
-        // part of a K row and its share of the V tile (both coalesced).
-        uint4 kreg[KV], vreg[KV];
-        if (sp < ntile) {
-            // the S threads of a position take every S-th 16-byte chunk of the row: their loads
-            // coalesce, and their reads of the queries below fall into different banks
-            const uint4 *kr = (const uint4 *)(a.kcache + (size_t)(tile + sp) * row_stride + head_off) + part;
-#pragma unroll
-            for (int c = 0; c < KV; ++c) kreg[c] = kr[c * S];
-        }
-#pragma unroll
-        for (int u = 0; u < KV; ++u) {
-            const int idx = tid + u * T, t = idx / (D / 8), c8 = idx % (D / 8);
-            vreg[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (t < ntile)
-                vreg[u] = *(const uint4 *)(a.vcache + (size_t)(tile + t) * row_stride + head_off + 8 * c8);
-        }
-        // scores: S threads per position, then a shuffle reduction among them
-        {
-            float s[kMaxGroup];
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) s[g] = 0.f;
-            if (sp < ntile) {
-#pragma unroll
-                for (int c = 0; c < KV; ++c) {
-                    const __half2 *kh = (const __half2 *)&kreg[c];
-                    float kf[8];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __half22float2(kh[e]);
-                        kf[2 * e] = f.x;
-                        kf[2 * e + 1] = f.y;
-                    }
-                    const int c0 = 8 * (c * S + part);
-#pragma unroll
-                    for (int g = 0; g < kMaxGroup; ++g) {
-                        if (g < G) {
-                            const float4 qa = *(const float4 *)&qs[g][c0], qb = *(const float4 *)&qs[g][c0 + 4];
-                            s[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x +
-                                    kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) {
-#pragma unroll
-                for (int dd = 1; dd < S; dd <<= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], dd);
-                if (sp >= ntile) s[g] = -INFINITY;
-            }
-            if (part == 0) {
-#pragma unroll
-                for (int g = 0; g < kMaxGroup; ++g) pw[sp][g] = s[g];
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < KV; ++u) ((uint4 *)vs)[tid + u * T] = vreg[u];
-        __syncthreads();
-        // running max and sum per head; scores become weights
-        for (int g = warp; g < G; g += T / 32) {
-            float sv[D / 32], tmax = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < D / 32; ++i) {
-                sv[i] = pw[lane + 32 * i][g];
-                tmax = fmaxf(tmax, sv[i]);
-            }
-            tmax = warp_max(tmax);
-            const float mold = m_run[g], mnew = fmaxf(mold, tmax);
-            float psum = 0.f;
-#pragma unroll
-            for (int i = 0; i < D / 32; ++i) {
-                const float p = expf(sv[i] - mnew);       // exp(-inf) = 0 for the positions past the tile
-                pw[lane + 32 * i][g] = p;
-                psum += p;
-            }
-            psum = warp_sum(psum);
-            if (lane == 0) {
-                const float al = expf(mold - mnew);        // 0 on the first tile (mold = -inf)
-                alpha[g] = al;
-                m_run[g] = mnew;
-                l_run[g] = l_run[g] * al + psum;
-            }
-        }
-        __syncthreads();
-        // weighted sum of V from shared memory: thread = (channel, group of positions)
-        {
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) acc[g] *= alpha[g];
-            const int tb = pg * (D / S), te = min(ntile, tb + D / S);
-#pragma unroll 8
-            for (int t = tb; t < te; ++t) {
-                const float v = __half2float(vs[t * D + ch]);
-                const float4 pa = *(const float4 *)&pw[t][0], pb = *(const float4 *)&pw[t][4];
-                acc[0] += pa.x * v; acc[1] += pa.y * v; acc[2] += pa.z * v; acc[3] += pa.w * v;
-                acc[4] += pb.x * v; acc[5] += pb.y * v; acc[6] += pb.z * v; acc[7] += pb.w * v;
-            }
-        }
-        __syncthreads();
-    }
-    // the S groups' sums of a channel meet in shared memory (the V tile is free now)
-    if (S > 1) {
-        float *part_acc = (float *)vs;           // [S - 1][kMaxGroup][D]
-        if (pg > 0) {
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) part_acc[((pg - 1) * kMaxGroup + g) * D + ch] = acc[g];
-        }
-        __syncthreads();
-        if (pg == 0) {
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g)
-#pragma unroll
-                for (int o = 0; o < S - 1; ++o) acc[g] += part_acc[(o * kMaxGroup + g) * D + ch];
-        }
-    }
-    // publish this split (threads of the first group: one per channel)
-    float *mine = a.partial + ((size_t)hk * nsplit + split) * G * (D + 2);
-    if (tid < D) {
-        for (int g = 0; g < G; ++g) {
-            mine[(size_t)g * (D + 2) + tid] = acc[g];
-            if (tid == 0) {
-                mine[(size_t)g * (D + 2) + D] = m_run[g];
-                mine[(size_t)g * (D + 2) + D + 1] = l_run[g];
-            }
-        }
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned old = atomicAdd(&a.counters[hk], 1u);
-        is_last = (old + 1u == (unsigned)nsplit);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // merge of the splits: thread = (channel, head phase), the heads are dealt out over the S
-    // groups.  A thread loads its channel's partial sums and the (max, sum) pairs of all splits
-    // at once (one round trip), forms the weights exp(max_s - max) itself and writes fp16.
-    const float *base = a.partial + (size_t)hk * nsplit * G * (D + 2);
-    for (int g = pg; g < G; g += S) {
-        float M = -INFINITY;
-        for (int s0 = 0; s0 < nsplit; s0 += 16) {
-            float ov[16], mv[16], lv[16];
-#pragma unroll
-            for (int u = 0; u < 16; ++u) {
-                const int s = min(s0 + u, nsplit - 1);
-                const float *p = base + ((size_t)s * G + g) * (D + 2);
-                ov[u] = __ldcg(p + ch);
-                mv[u] = __ldcg(p + D);
-                lv[u] = s0 + u < nsplit ? __ldcg(p + D + 1) : 0.f;
-            }
-            float Mc = M;
-#pragma unroll
-            for (int u = 0; u < 16; ++u) Mc = fmaxf(Mc, mv[u]);
-            // running rescale across chunks of 16 splits (one chunk for caches up to 2048 positions)
-            const float r = s0 ? expf(M - Mc) : 0.f;
-            if (s0 == 0) {
-                acc[0] = 0.f;
-                acc[1] = 0.f;
-            }
-            acc[0] *= r;
-            acc[1] *= r;
-#pragma unroll
-            for (int u = 0; u < 16; ++u) {
-                const float w = s0 + u < nsplit ? expf(mv[u] - Mc) : 0.f;
-                acc[0] += ov[u] * w;          // weighted output of this channel
-                acc[1] += lv[u] * w;          // weighted sum of the softmax denominators
-            }
-            M = Mc;
-        }
-        a.out[(size_t)(hk * G + g) * D + ch] = __float2half_rn(acc[0] / acc[1]);
-    }
-    if (tid == 0) a.counters[hk] = 0u;
+    attention_unit<D, S>(a, blockIdx.x, blockIdx.y, gridDim.y, sm, threadIdx.x, [] { __syncthreads(); });
 }
+
+}  // namespace
 
 // splits per kv head for a cache of max_ctx positions: about one CTA per SM, at least 128
 // positions each, at most kMaxSplits
@@ -483,7 +210,6 @@ int attention_splits(int head_kv, int max_ctx) {
     return s;
 }
 
-}  // namespace
 }  // namespace hlq
 
 using namespace hlq;

@@ -27,6 +27,33 @@ struct hlq_weight {
 
 namespace hlq {
 
+constexpr int kDefaultSpinLimit = 1 << 22;   // polls of one bounded wait unless the caller sets another
+
+// Peer-mapped buffers of a fused all-reduce (one per tensor-parallel communicator), in device
+// memory.  recv[p] is rank p's receive buffer as mapped into this
+// process; slot (parity, source rank, row of x, output row or block).
+struct TpDev {
+    unsigned long long *recv[8];   // slots of (launch number << 32 | fp32 bits): value and flag are one 64-bit word
+    unsigned *seq;        // number of finished fused launches on this rank
+    unsigned *done;       // blocks summed so far in the current launch
+    int rank, world, max_m, np_cap;
+};
+
+}  // namespace hlq
+
+struct hlq_tp_comm {
+    int device = 0, rank = 0, world = 1, max_m = 1, np_cap = 0;
+    unsigned char *local = nullptr;      // this rank's receive buffer, flags, counters (cudaMalloc)
+    size_t bytes = 0, seq_off = 0;
+    void *peer[8] = {};                  // every rank's buffer as mapped here
+    hlq::TpDev *d_tp = nullptr;
+    bool connected = false;
+    bool ipc = false;                    // peer[] came from cudaIpcOpenMemHandle
+    int spin_limit = hlq::kDefaultSpinLimit;
+};
+
+namespace hlq {
+
 // Records a failing CUDA call for hlq_last_cuda_error(); returns HLQ_ERR_CUDA or HLQ_OK.
 int note_cuda(cudaError_t e);
 void count_launch(int n = 1);
@@ -55,6 +82,8 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
                      const hlq_input_op *op = nullptr);
 int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
                      void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// Splits of the context per kv head the attention kernel uses for a cache of max_ctx positions.
+int attention_splits(int head_kv, int max_ctx);
 int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, void *y,
                         int y_dtype, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream);

@@ -61,7 +61,7 @@ class TPDecoder:
     def __init__(self, cfg: DecoderConfig, device: torch.device, rank: int = 0, world: int = 1,
                  group=None, seed: int = 0, grouped: bool = True, fused_allreduce: bool = False,
                  fused_glue: bool = True, quantized_lm_head: bool = True, fused_inputs: bool = False,
-                 kv_head_major: bool = True, export=None):
+                 kv_head_major: bool = True, export=None, chain: bool = False):
         if cfg.n_heads % world or cfg.n_kv % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, kv heads, ffn and vocab must split evenly over the ranks")
         self.cfg, self.dev, self.rank, self.world, self.group = cfg, device, rank, world, group
@@ -72,16 +72,55 @@ class TPDecoder:
         rows, cols = _lib.HLQ_SHARD_ROWS, _lib.HLQ_SHARD_COLS
         self.layers = []
         self.linear_bytes = 0
+        # one persistent kernel for all layers (chain.py): needs the package's glue and 128-wide heads
+        self.use_chain = bool(chain and fused_glue and c.head_dim == 128 and (c.ffn // world) % 16 == 0)
 
-        def load(n, k, mode, lseed, bits=c.bits, groupsize=c.groupsize, given=None):
+        def source(n, k, lseed, bits=c.bits, groupsize=c.groupsize, given=None):
             if given is not None:           # a linear of an exported model (host arrays)
                 if given.out_channel != n or given.in_channel != k:
                     raise ValueError(f"exported linear is {given.out_channel}x{given.in_channel}, expected {n}x{k}")
-                lin = given
-            else:
-                gen.manual_seed(lseed)      # every rank draws the full tensor and keeps its shard
-                lin = _random_export(n, k, bits, groupsize, gen, device)
+                return given
+            gen.manual_seed(lseed)          # every rank draws the full tensor and keeps its shard
+            return _random_export(n, k, bits, groupsize, gen, device)
+
+        def load(n, k, mode, lseed, bits=c.bits, groupsize=c.groupsize, given=None):
+            lin = source(n, k, lseed, bits, groupsize, given)
             w = HLQWeight.from_export(lin, device=device.index, tp_rank=rank, tp_size=world, shard_mode=mode)
+            self.linear_bytes += w.info.algorithmic_bytes
+            return w
+
+        def load_gate_up(lseed_gate, lseed_up, given_gate, given_up):
+            """This rank's gate and up rows as ONE weight whose rows alternate in chunks of 16
+            (16 gate rows, the 16 up rows of the same ffn channels): the chain applies the gated
+            SiLU where it completes such a block."""
+            from .chain import interleave_rows
+            fl = c.ffn // world
+            lo, hi = rank * fl, (rank + 1) * fl
+            g_lin = source(c.ffn, c.hidden, lseed_gate, given=given_gate)
+            parts = [g_lin.w_quant[:, lo:hi], g_lin.w_scale[:, lo:hi], g_lin.w_zero[lo:hi]]
+            del g_lin
+            u_lin = source(c.ffn, c.hidden, lseed_up, given=given_up)
+            fused = ExportedLinear(interleave_rows(parts[0], u_lin.w_quant[:, lo:hi], 1),
+                                   interleave_rows(parts[1], u_lin.w_scale[:, lo:hi], 1),
+                                   interleave_rows(parts[2], u_lin.w_zero[lo:hi], 0), None, u_lin.groupsize)
+            del u_lin, parts
+            w = HLQWeight.from_export(fused, device=device.index)
+            self.linear_bytes += w.info.algorithmic_bytes
+            return w
+
+        def load_qkv(lseeds, givens):
+            """This rank's q, k and v rows as ONE weight (rows q | k | v): one linear, one stage."""
+            parts = []
+            for (n, lseed, given) in zip((q_dim, kv_dim, kv_dim), lseeds, givens):
+                lin = source(n, c.hidden, lseed, given=given)
+                lo, hi = rank * (n // world), (rank + 1) * (n // world)
+                parts.append((lin.w_quant[:, lo:hi], lin.w_scale[:, lo:hi], lin.w_zero[lo:hi], lin.groupsize))
+                del lin
+            cat = (lambda ts, ax: torch.cat(ts, dim=ax).contiguous()) if isinstance(parts[0][0], torch.Tensor) else \
+                (lambda ts, ax: __import__("numpy").ascontiguousarray(__import__("numpy").concatenate(ts, axis=ax)))
+            fused = ExportedLinear(cat([p[0] for p in parts], 1), cat([p[1] for p in parts], 1),
+                                   cat([p[2] for p in parts], 0), None, parts[0][3])
+            w = HLQWeight.from_export(fused, device=device.index)
             self.linear_bytes += w.info.algorithmic_bytes
             return w
 
@@ -90,15 +129,20 @@ class TPDecoder:
             s0 = seed + li * 16
             ex = export.layers[li] if export is not None else None
             giv = (lambda name: ex.linears[name]) if ex is not None else (lambda name: None)
-            L = {
-                "q": load(q_dim, c.hidden, rows, s0 + 0, given=giv("q")),
-                "k": load(kv_dim, c.hidden, rows, s0 + 1, given=giv("k")),
-                "v": load(kv_dim, c.hidden, rows, s0 + 2, given=giv("v")),
-                "o": load(c.hidden, q_dim, cols, s0 + 3, given=giv("o")),
-                "gate": load(c.ffn, c.hidden, rows, s0 + 4, given=giv("gate")),
-                "up": load(c.ffn, c.hidden, rows, s0 + 5, given=giv("up")),
-                "down": load(c.hidden, c.ffn, cols, s0 + 6, given=giv("down")),
-            }
+            L = {}
+            if self.use_chain:
+                L["qkv_w"] = load_qkv((s0 + 0, s0 + 1, s0 + 2), (giv("q"), giv("k"), giv("v")))
+            else:
+                L["q"] = load(q_dim, c.hidden, rows, s0 + 0, given=giv("q"))
+                L["k"] = load(kv_dim, c.hidden, rows, s0 + 1, given=giv("k"))
+                L["v"] = load(kv_dim, c.hidden, rows, s0 + 2, given=giv("v"))
+            L["o"] = load(c.hidden, q_dim, cols, s0 + 3, given=giv("o"))
+            L["down"] = load(c.hidden, c.ffn, cols, s0 + 6, given=giv("down"))
+            if self.use_chain:
+                L["gate_up"] = load_gate_up(s0 + 4, s0 + 5, giv("gate"), giv("up"))
+            else:
+                L["gate"] = load(c.ffn, c.hidden, rows, s0 + 4, given=giv("gate"))
+                L["up"] = load(c.ffn, c.hidden, rows, s0 + 5, given=giv("up"))
             gen.manual_seed(s0 + 7)
             if ex is not None:
                 L["ln1"] = torch.from_numpy(ex.ln1.astype("float16")).to(device)
@@ -123,9 +167,9 @@ class TPDecoder:
             del kfull, vfull
             # buffers
             L["xn"] = torch.empty((1, c.hidden), dtype=dt, device=device)
-            L["q_o"] = torch.empty((1, self.hq * c.head_dim), dtype=dt, device=device)
-            L["k_o"] = torch.empty((1, self.hkv * c.head_dim), dtype=dt, device=device)
-            L["v_o"] = torch.empty((1, self.hkv * c.head_dim), dtype=dt, device=device)
+            nq, nkv = self.hq * c.head_dim, self.hkv * c.head_dim
+            L["qkv_o"] = torch.empty((1, nq + 2 * nkv), dtype=dt, device=device)       # q | k | v of this rank
+            L["q_o"], L["k_o"], L["v_o"] = L["qkv_o"][:, :nq], L["qkv_o"][:, nq:nq + nkv], L["qkv_o"][:, nq + nkv:]
             L["att"] = torch.empty((1, self.hq * c.head_dim), dtype=dt, device=device)
             L["o_o"] = torch.empty((1, c.hidden), dtype=dt, device=device)
             L["xn2"] = torch.empty((1, c.hidden), dtype=dt, device=device)
@@ -135,7 +179,7 @@ class TPDecoder:
             L["d_o"] = torch.empty((1, c.hidden), dtype=dt, device=device)
             L["r1"] = torch.empty((1, c.hidden), dtype=dt, device=device)   # residual stream after attention's add
             L["r2"] = torch.empty((1, c.hidden), dtype=dt, device=device)   # ... after the MLP's add
-            if grouped:
+            if grouped and not self.use_chain:
                 L["qkv"] = HLQGroup([L["q"], L["k"], L["v"]], max_m=1)
                 L["gu"] = HLQGroup([L["gate"], L["up"]], max_m=1)
             self.layers.append(L)
@@ -191,11 +235,11 @@ class TPDecoder:
         self.x = torch.empty((1, c.hidden), dtype=dt, device=device)
         self.xfinal = torch.empty((1, c.hidden), dtype=dt, device=device)
         # norms and SiLU folded into the table build of the linear that follows them
-        self.fused_inputs = bool(fused_inputs and fused_glue and grouped and quantized_lm_head)
+        self.fused_inputs = bool(fused_inputs and fused_glue and grouped and quantized_lm_head and not self.use_chain)
         self._ops = []                       # keeps the op structs (and through them nothing else) alive
         prev_delta, prev_res = None, self.x
         for L in self.layers:
-            if not grouped:
+            if not grouped or self.use_chain:
                 break
             if self.fused_inputs:
                 from .linear import input_op
@@ -225,9 +269,37 @@ class TPDecoder:
         self.graph = None
         # all-reduce of o / down inside the GEMV kernel instead of a separate NCCL launch
         self.comm = None
-        if fused_allreduce and world > 1:
+        if (fused_allreduce or self.use_chain) and world > 1:      # the chain sums the ranks inside its kernel
             from .tp import FusedAllReduceComm
             self.comm = FusedAllReduceComm(max_n=c.hidden, max_m=1, device=device.index, group=group)
+        self.chain = None
+        if self.use_chain:
+            self._record_chain()
+
+    def _record_chain(self):
+        """All layers of one token as one persistent kernel: per layer the stages q/k/v ->
+        attention -> o (+ residual add) -> gate/up (+ gated SiLU) -> down (+ residual add); the
+        norms run in the table build of q/k/v and gate/up (the first layer's first norm, which has
+        no producer inside the chain, stays a kernel of its own)."""
+        from .chain import DecodeChain
+        c, I = self.cfg, _lib
+        ch = DecodeChain(self.dev, ss_cells=2 * len(self.layers))
+        x = self.x
+        for li, L in enumerate(self.layers):
+            if li == 0:
+                qkv_in = dict(x=L["xn"])
+            else:
+                qkv_in = dict(x=x, in_kind=I.HLQ_CHAIN_IN_NORM, gamma=L["ln1"], eps=1e-5, ss_in=2 * li - 1)
+            ch.add_linears([ch.linear(L["qkv_w"], y=L["qkv_o"], **qkv_in)])
+            ch.add_attention(self.attn, L["q_o"], L["k_o"], L["v_o"], L["kc"], L["vc"], self.position, L["att"])
+            ch.add_linears([ch.linear(L["o"], L["att"], x, in_kind=I.HLQ_CHAIN_IN_ATTENTION,
+                                      out_kind=I.HLQ_CHAIN_OUT_RESIDUAL, ss_out=2 * li)], comm=self.comm)
+            ch.add_linears([ch.linear(L["gate_up"], x, L["act"], in_kind=I.HLQ_CHAIN_IN_NORM, gamma=L["ln2"],
+                                      eps=1e-5, ss_in=2 * li, out_kind=I.HLQ_CHAIN_OUT_GATED_SILU)])
+            ch.add_linears([ch.linear(L["down"], L["act"], x, out_kind=I.HLQ_CHAIN_OUT_RESIDUAL, ss_out=2 * li + 1)],
+                           comm=self.comm)
+        ch.finish()
+        self.chain = ch
 
     @classmethod
     def from_export(cls, export, n_heads: int, n_kv: int, device, head_dim: int = None, ctx: int = 2048,
@@ -284,9 +356,27 @@ class TPDecoder:
     def step_eager(self, token=None):
         """One decode step on `token` (None: the id already in self.token); returns the next
         token id (greedy) as a device tensor."""
+        if self.use_chain:
+            return self._step_chain(token)
         if self.fused_inputs:
             return self._step_fused_inputs(token)
         return self._step_fused(token) if self.fused_glue else self._step_torch(token)
+
+    def _step_chain(self, token):
+        """5 launches per token: the first layer's first norm, the chain kernel (all layers), the
+        final norm, lm_head, argmax."""
+        from . import glue
+        if token is not None:
+            self.token.fill_(int(token))
+        torch.index_select(self.embed, 0, self.token, out=self.x)
+        xn = self.layers[0]["xn"]
+        glue.rmsnorm(self.x, self.layers[0]["ln1"], 1e-5, out=xn)
+        self.chain.forward()
+        glue.rmsnorm(self.x, self.norm, 1e-5, out=xn)
+        logits = self._logits(xn)
+        glue.argmax(logits.view(-1), self.next_index, self.next_value)
+        self.last_logits = logits
+        return self._pick(self.next_value, self.next_index)
 
     def _step_fused_inputs(self, token):
         """5 launches per layer: both norms (with their residual adds) and the gated SiLU run
@@ -451,6 +541,8 @@ class TPDecoder:
     def launches_per_step(self) -> int:
         """Kernels of this package in one step (the embedding copy, the lm_head product and the
         collectives are library calls and not counted)."""
+        if self.use_chain:
+            return 4 + (1 if self.lm_w is not None else 0)
         per_layer = (2 if self.grouped else 5) + 2          # qkv, gate/up (+ o, down below)
         if self.fused_inputs:
             per_layer += 1                                  # attention

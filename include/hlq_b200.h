@@ -370,6 +370,81 @@ int hlq_rope_cache_attention(const void *d_q, const void *d_k, const void *d_v, 
                              int dhead, int max_ctx, int kv_layout, float rotary_base, float scale,
                              void *d_out, void *d_workspace, size_t workspace_bytes, void *stream);
 
+/* ---- decode chain: one token's ops of all layers as one persistent kernel ----------------
+ *
+ * The reference's model runs one call per op and token (C++/examples/models/llama.cpp:185-700:
+ * per layer RMSNorm, q/k/v, RoPE, cache append, attention, o, residual add + RMSNorm, gate/up,
+ * gated SiLU, down).  A chain is that list of ops recorded once and then run, for every token,
+ * by ONE kernel whose CTAs stay resident: a STAGE is a set of linears whose inputs are ready
+ * together (hlq_chain_add_linears) or the attention of one token (hlq_chain_add_attention);
+ * stage s + 1 starts reading when stage s has written everything (a counter in device memory,
+ * polled with a bounded wait).  The elementwise ops sit in the linears:
+ *   input   HLQ_CHAIN_IN_PLAIN     x = the fp16 activations [k];
+ *           HLQ_CHAIN_IN_NORM      x = the residual stream [k]; the tables are built from
+ *                                  fp16(x * gamma / sqrt(cell[ss_in] / norm_channels + eps)),
+ *                                  where the cell was filled by the stage that last updated the stream
+ *                                  (launch_rms_norm / launch_pre_rms_norm, arm_rmsnorm.cpp:25-41, 68-85);
+ *           HLQ_CHAIN_IN_ATTENTION x = the output of the attention stage recorded just before (d_x is
+ *                                  ignored): the attention units leave one partial result per split of the
+ *                                  context, and this linear merges them while it loads its activations
+ *                                  (the merge of arm_attention.cpp:320-340's per-head results, without a pass
+ *                                  or a hand-off of its own); k must be head_q * 128;
+ *   output  HLQ_CHAIN_OUT_STORE    y[n] = fp16(result);
+ *           HLQ_CHAIN_OUT_RESIDUAL y is the residual stream: t = y + fp16(result), y = fp16(t),
+ *                                  cell[ss_out] += sum t^2                  (arm_rmsnorm.cpp:68-85);
+ *           HLQ_CHAIN_OUT_GATED_SILU the weight's rows alternate in chunks of 16 between gate rows
+ *                                  and up rows (rows 32c..32c+15 = gate 16c..16c+15, rows 32c+16..32c+31
+ *                                  = up 16c..16c+15); y[n/2] = fp16(up * gate / (1 + exp(-gate)))
+ *                                  (gated_silu, arm_activation.cpp:36-49).
+ * With a communicator (one linear per stage, HLQ_SHARD_COLS weight) the ranks' results are summed
+ * inside the kernel before the output op, as in hlq_linear_forward_allreduce; every rank must
+ * record the same chain.  All members share bits and group size, use the streaming layout and
+ * fp16 activations, batch 1.  The chain owns its scratch; weights, buffers and the communicator
+ * must outlive it.  hlq_chain_forward clears the chain's counters on `stream` and launches the
+ * kernel (no allocation; it can be captured into a CUDA graph).  hlq_chain_status reads the
+ * status word (1: a wait ran out, 2: shared-memory window unusable) as hlq_workspace_status does. */
+typedef struct hlq_chain hlq_chain;
+typedef enum hlq_chain_in { HLQ_CHAIN_IN_PLAIN = 0, HLQ_CHAIN_IN_NORM = 1, HLQ_CHAIN_IN_ATTENTION = 2 } hlq_chain_in;
+typedef enum hlq_chain_out {
+    HLQ_CHAIN_OUT_STORE = 0,
+    HLQ_CHAIN_OUT_RESIDUAL = 1,
+    HLQ_CHAIN_OUT_GATED_SILU = 2
+} hlq_chain_out;
+typedef struct hlq_chain_linear {
+    const hlq_weight *w;
+    const void *d_x;      /* fp16 [k], 16-byte aligned */
+    void *d_y;            /* fp16: [n], the residual stream [n], or [n/2] (see hlq_chain_out) */
+    int in_kind;          /* hlq_chain_in */
+    int out_kind;         /* hlq_chain_out */
+    const void *d_gamma;  /* IN_NORM: fp16 [k], 16-byte aligned */
+    float eps;            /* IN_NORM */
+    int norm_channels;    /* IN_NORM: channels the sum of squares covers (0: k) */
+    int ss_in;            /* IN_NORM: cell to read */
+    int ss_out;           /* OUT_RESIDUAL: cell to accumulate into */
+} hlq_chain_linear;
+int hlq_chain_create(hlq_chain **out, int device, int ss_cells);
+int hlq_chain_add_linears(hlq_chain *c, int count, const hlq_chain_linear *members, hlq_tp_comm *comm_or_null);
+/* Arguments as hlq_rope_cache_attention (dhead 128 only; all attention stages of a chain share d_position,
+ * rotary_base and max_ctx).  d_out is written only by hlq_rope_cache_attention: in a chain the stage's
+ * result is consumed by the next stage's linear through HLQ_CHAIN_IN_ATTENTION. */
+int hlq_chain_add_attention(hlq_chain *c, const void *d_q, const void *d_k, const void *d_v, void *d_kcache,
+                            void *d_vcache, const int *d_position, int head_q, int head_kv, int dhead,
+                            int max_ctx, int kv_layout, float rotary_base, float scale, void *d_out,
+                            void *d_workspace, size_t workspace_bytes);
+/* Ends the recording: allocates the scratch and uploads the tables (synchronizes `stream`). */
+int hlq_chain_finish(hlq_chain *c, void *stream);
+int hlq_chain_forward(hlq_chain *c, void *stream);
+int hlq_chain_status(const hlq_chain *c, void *stream, int *kernel_status);
+/* Profiling aid: with a device buffer of ctas x items_per_cta x 16 uint64 (zeroed by the caller), the
+ * next forwards write a timeline into it: for item i of CTA c, entry [c][i][k] is the nanosecond clock when
+ * (k = 0) the control warp saw the item's gate open, (1) had issued its input copies, (2, 3) the consumers
+ * began and ended waiting for the inputs, (4) agreed to run, (5) had built the tables, (6) ended streaming,
+ * (7) handed the item over, (8, 9, 10) the finalizers took it, had published it, had summed the ranks.
+ * d_trace NULL or items_per_cta 0 turns it off.  *ctas receives the grid size. */
+int hlq_chain_trace(hlq_chain *c, void *d_trace, int items_per_cta, int *ctas);
+int hlq_chain_info(const hlq_chain *c, int *stages, int *linears, int *rank_sums, int64_t *scratch_bytes);
+int hlq_chain_free(hlq_chain *c);
+
 /* ---- diagnostics -------------------------------------------------------------------- */
 
 /* Human-readable text for an hlq_status.  Replaces the reference's exit(-1)/exceptions

@@ -1,0 +1,88 @@
+"""The decode chain (all layers of one token as one persistent kernel) against the same decoder
+run as one launch per op.  Both use the same seeded weights; the chain fuses gate/up into one
+weight with interleaved rows, applies norms, residual adds and the gated SiLU inside its
+linears, and hands stages over through counters in device memory."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def _decoders(seed, **kw):
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    dev = torch.device("cuda", 0)
+    a = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=seed, chain=True, **kw)
+    b = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=seed, chain=False, **kw)
+    assert a.use_chain and a.chain is not None and not b.use_chain
+    return a, b
+
+
+@pytest.mark.timeout(120)
+def test_chain_step_equals_the_step_of_separate_launches():
+    a, b = _decoders(seed=17)
+    info = a.chain.info()
+    assert info["stages"] == 5 * len(a.layers) and info["linears"] == 4 * len(a.layers)
+    assert a.launches_per_step() < b.launches_per_step()
+    for step in range(3):                      # the chain's counters and cells are cleared every token
+        ta, tb = a.step_eager(7 + step), b.step_eager(7 + step)
+        torch.cuda.synchronize()
+        assert a.chain.status() == 0 and a.attn.status() == 0
+        xa, xb = a.hidden_after_step().float(), b.hidden_after_step().float()
+        assert (xa - xb).abs().max() / xb.abs().max() <= 4e-3, step
+        la, lb = a.last_logits.float(), b.last_logits.float()
+        assert (la - lb).abs().max() / lb.abs().max() <= 1e-2
+        top2 = torch.topk(lb.view(-1), 2).values
+        if float(top2[0] - top2[1]) > 2e-2 * float(lb.abs().max()):
+            assert int(ta.item()) == int(tb.item())
+    # the cache rows the steps appended agree (v bit-exactly unless an fp16 rounding moved upstream)
+    pos = a.pos
+    for La, Lb in zip(a.layers, b.layers):
+        va, vb = a.kv_rows(La, "vc", pos, pos + 1), b.kv_rows(Lb, "vc", pos, pos + 1)
+        assert (va.float() - vb.float()).abs().max() <= 3e-2
+
+
+@pytest.mark.timeout(120)
+def test_chain_in_a_graph_generates_the_same_tokens():
+    a, b = _decoders(seed=23)
+    ta = a.generate(3, 6, start_position=100, use_graph=True)
+    tb = b.generate(3, 6, start_position=100, use_graph=False)
+    assert a.chain.status() == 0
+    assert ta == tb and len(ta) == 6
+    for La, Lb in zip(a.layers, b.layers):
+        assert (a.kv_rows(La, "kc", 100, 106).float() - b.kv_rows(Lb, "kc", 100, 106).float()).abs().max() <= 3e-2
+        assert torch.equal(a.kv_rows(La, "kc", 106, 256), b.kv_rows(Lb, "kc", 106, 256))
+
+
+@pytest.mark.timeout(120)
+def test_chain_request_falls_back_where_the_kernel_does_not_apply(tmp_path):
+    """The golden directory written by the reference's quantizer driver has heads of 64
+    channels; the chain runs 128-channel heads only, so asking for it must quietly give the
+    path of separate launches, with the reference model's logits."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    from elutq_b200.decoder import TPDecoder
+    d = np.load(os.path.join(ROOT, "tests", "golden", "model_tiny_llama.npz"))
+    for key in d.files:
+        if key.startswith("file:"):
+            p = tmp_path / key[5:]
+            p.parent.mkdir(parents=True, exist_ok=True)
+            p.write_bytes(d[key].tobytes())
+    dec = TPDecoder.from_export(str(tmp_path), n_heads=int(d["n_heads"]), n_kv=int(d["n_kv"]),
+                                device=torch.device("cuda", 0), ctx=64, rope_theta=float(d["rope_theta"]), chain=True)
+    assert not dec.use_chain and dec.chain is None
+    dec.position.fill_(0)
+    dec.step_eager(int(d["tokens"][0]))
+    torch.cuda.synchronize()
+    ref = d["logits"][0].astype(np.float64)
+    got = dec.last_logits.float().cpu().numpy()[0].astype(np.float64)
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2

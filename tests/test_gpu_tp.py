@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, init_file, out_dir):
+def _worker(rank, world, init_file, out_dir, chain=False):
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch.distributed as dist
@@ -24,9 +24,13 @@ def _worker(rank, world, init_file, out_dir):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world, device_id=dev)
     try:
-        dec = TPDecoder(PRESETS["tiny"], dev, rank, world, seed=3)
-        dec.step_eager(5)
+        dec = TPDecoder(PRESETS["tiny"], dev, rank, world, seed=3, chain=chain)
+        assert dec.use_chain == chain
+        for tok in (5, 9, 2):               # several tokens: the rank sums' tags and slot sets alternate
+            dec.step_eager(tok)
         torch.cuda.synchronize()
+        if chain:
+            assert dec.chain.status() == 0 and dec.chain.info()["rank_sums"] == 2 * len(dec.layers)
         if rank == 0:
             np.save(os.path.join(out_dir, "x_tp.npy"), dec.hidden_after_step().float().cpu().numpy())
             np.save(os.path.join(out_dir, "tok_tp.npy"), dec.next_token.cpu().numpy())
@@ -49,10 +53,34 @@ def test_two_gpu_decode_matches_one_gpu():
         tok_tp = np.load(os.path.join(tmp, "tok_tp.npy"))
     dev = torch.device("cuda", 0)
     one = TPDecoder(PRESETS["tiny"], dev, 0, 1, seed=3)
-    one.step_eager(5)
+    for tok in (5, 9, 2):
+        one.step_eager(tok)
     torch.cuda.synchronize()
     x1 = one.hidden_after_step().float().cpu().numpy()
     # fp16 activations between the layers: the two runs round at different places
+    assert np.abs(x_tp - x1).max() / np.abs(x1).max() <= 1e-2
+    assert int(tok_tp[0]) == int(one.next_token[0])
+
+
+@pytest.mark.timeout(150)
+def test_two_gpu_decode_chain_matches_one_gpu():
+    """The decode chain (one persistent kernel per rank, rank sums of o and down inside it)
+    on two GPUs against the decoder of separate launches on one GPU."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    sys.path.insert(0, ROOT)
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker, args=(2, os.path.join(tmp, "init"), tmp, True), nprocs=2, join=True)
+        x_tp = np.load(os.path.join(tmp, "x_tp.npy"))
+        tok_tp = np.load(os.path.join(tmp, "tok_tp.npy"))
+    one = TPDecoder(PRESETS["tiny"], torch.device("cuda", 0), 0, 1, seed=3)
+    for tok in (5, 9, 2):
+        one.step_eager(tok)
+    torch.cuda.synchronize()
+    x1 = one.hidden_after_step().float().cpu().numpy()
     assert np.abs(x_tp - x1).max() / np.abs(x1).max() <= 1e-2
     assert int(tok_tp[0]) == int(one.next_token[0])
 
