@@ -100,6 +100,7 @@ static void free_buffers(hlq_weight *w) {
     if (w->d_bias) cudaFree(w->d_bias);
     if (w->d_status) cudaFree(w->d_status);
     w->d_status = nullptr;
+    free_sparse(w);
     w->d_planes = nullptr;
     w->d_meta = nullptr;
     w->d_bias = nullptr;
@@ -168,6 +169,7 @@ int hlq_weight_from_export(hlq_weight **out, const void *w_quant, const void *w_
     w->device = device;
     w->n = sp.n; w->k = sp.k; w->g = g; w->q = q;
     w->n_full = out_ch; w->k_full = in_ch;
+    w->n0 = sp.n0; w->k0 = sp.k0;
     w->tp_rank = tp_rank; w->tp_size = tp_size; w->shard_mode = tp_size > 1 ? shard_mode : HLQ_SHARD_NONE;
     w->layout = (stream_supported(g) && !(flags & HLQ_FLAG_FORCE_EXPORT_LAYOUT)) ? HLQ_LAYOUT_STREAM
                                                                                  : HLQ_LAYOUT_EXPORT;
@@ -341,6 +343,7 @@ int hlq_linear_forward_op(int m, int k, int n, const void *d_x, int x_dtype, voi
     if (!d_x || !d_y) return HLQ_ERR_INVALID_ARGUMENT;
     if (m > hlq::kLutMaxM) return HLQ_ERR_UNSUPPORTED;
     if (y_dtype != HLQ_F16 && y_dtype != HLQ_BF16 && y_dtype != HLQ_F32) return HLQ_ERR_UNSUPPORTED;
+    if (w->sp_pairs && op && op->kind != HLQ_INPUT_PLAIN) return HLQ_ERR_UNSUPPORTED;   // the plane sees plain x
     int cur = -1;
     HLQ_CUDA(cudaGetDevice(&cur));
     if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;
@@ -370,12 +373,17 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
         if (w->layout == HLQ_LAYOUT_EXPORT) impl = 2;
         else impl = (m <= kLutMaxM || (m <= 2 * kLutMaxM && y_dtype != HLQ_F32)) ? 1 : 3;
     }
+    int rc;
     switch (impl) {
+        // the LUT GEMV takes the extra bit-plane into its accumulators before it runs
         case 1: return launch_lut8_gemv(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream);
-        case 2: return launch_lut4_gemv(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream);
-        case 3: return launch_dequant_gemm(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream);
+        case 2: rc = launch_lut4_gemv(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream); break;
+        case 3: rc = launch_dequant_gemm(w, m, d_x, x_dtype, d_y, y_dtype, d_workspace, workspace_bytes, stream); break;
         default: return HLQ_ERR_INVALID_ARGUMENT;
     }
+    // the other kernels: the extra bit-plane is added to y afterwards
+    if (!rc && w->sp_pairs) rc = launch_sparse_plane(w, m, d_x, x_dtype, nullptr, 0, d_y, y_dtype, stream);
+    return rc;
 }
 
 int hlq_linear_forward(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,

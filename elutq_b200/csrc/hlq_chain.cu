@@ -846,7 +846,7 @@ int hlq_chain_add_linears(hlq_chain *c, int count, const hlq_chain_linear *m, hl
         const hlq_weight *w = m[i].w;
         if (!w || !m[i].d_y) return HLQ_ERR_INVALID_ARGUMENT;
         if (!m[i].d_x && m[i].in_kind != HLQ_CHAIN_IN_ATTENTION) return HLQ_ERR_INVALID_ARGUMENT;
-        if (w->layout != HLQ_LAYOUT_STREAM || w->device != c->device) return HLQ_ERR_UNSUPPORTED;
+        if (w->layout != HLQ_LAYOUT_STREAM || w->device != c->device || w->sp_pairs) return HLQ_ERR_UNSUPPORTED;
         if (c->q == 0) {
             c->q = w->q;
             c->g = w->g;

@@ -1049,6 +1049,9 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         a.one_row_passes = a.single.xop != HLQ_INPUT_PLAIN;
         int ctas = force_ctas > 0 ? force_ctas : di->sms;
         if ((long long)d.slices * d.duos < ctas) ctas = d.slices * d.duos;
+        // a weight with the extra bit-plane: its blocks' sums go into the accumulators first
+        rc = launch_sparse_plane(w, mc, a.single.x, x_dtype, ws.partial, d.np, nullptr, y_dtype, stream);
+        if (rc) return rc;
         rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream);
         if (rc) return rc;
     }
@@ -1086,7 +1089,7 @@ static int static_scratch_address(int device, void **out) {
 
 int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dtype, void *y,
                             int y_dtype, cudaStream_t stream) {
-    if (w->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
+    if (w->layout != HLQ_LAYOUT_STREAM || w->sp_pairs) return HLQ_ERR_UNSUPPORTED;
     if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)y & 3)) return HLQ_ERR_ALIGNMENT;
     const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
@@ -1302,7 +1305,7 @@ int hlq_linear_forward_allreduce_op(int m, int k, int n, const void *d_x, int x_
     if (m == 0) return HLQ_OK;
     if (!d_x || !d_y) return HLQ_ERR_INVALID_ARGUMENT;
     if (!comm->connected || comm->device != w->device) return HLQ_ERR_INVALID_ARGUMENT;
-    if (w->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
+    if (w->layout != HLQ_LAYOUT_STREAM || w->sp_pairs) return HLQ_ERR_UNSUPPORTED;
     if (x_dtype != HLQ_F16 && x_dtype != HLQ_BF16) return HLQ_ERR_UNSUPPORTED;
     if (y_dtype != HLQ_F16 && y_dtype != HLQ_BF16 && y_dtype != HLQ_F32) return HLQ_ERR_UNSUPPORTED;
     if (((uintptr_t)d_x & 15) || ((uintptr_t)d_y & 3)) return HLQ_ERR_ALIGNMENT;
@@ -1360,7 +1363,7 @@ int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weight
     if (count <= 0 || !weights || max_m < 1 || max_m > kLutMaxM) return HLQ_ERR_INVALID_ARGUMENT;
     for (int i = 0; i < count; ++i) {
         if (!weights[i]) return HLQ_ERR_INVALID_ARGUMENT;
-        if (weights[i]->layout != HLQ_LAYOUT_STREAM) return HLQ_ERR_UNSUPPORTED;
+        if (weights[i]->layout != HLQ_LAYOUT_STREAM || weights[i]->sp_pairs) return HLQ_ERR_UNSUPPORTED;
         if (weights[i]->q != weights[0]->q || weights[i]->g != weights[0]->g ||
             weights[i]->device != weights[0]->device)
             return HLQ_ERR_UNSUPPORTED;

@@ -10,6 +10,7 @@ struct hlq_weight {
     int device = 0;
     int n = 0, k = 0, g = 0, q = 0;  // this shard
     int n_full = 0, k_full = 0;
+    int n0 = 0, k0 = 0;              // offsets of this shard in the full weight
     int tp_rank = 0, tp_size = 1, shard_mode = 0;
     int layout = HLQ_LAYOUT_STREAM;
     // HLQ_LAYOUT_STREAM: planes = streaming cells, meta = streaming scales/zeros.
@@ -23,6 +24,12 @@ struct hlq_weight {
     // word when a forward call brings no workspace (allocated with the handle, never in a
     // launch path).
     int *d_status = nullptr;
+    // optional extra bit-plane of the runtime's "sparse" weights: blocks of 32 rows x one group,
+    // kept in exported order (coordinates of this shard)
+    int sp_pairs = 0;
+    uint32_t *d_sp_mask = nullptr;   // [pairs][2]
+    uint8_t *d_sp_blocks = nullptr;  // [pairs][32][g/8]
+    uint16_t *d_sp_scales = nullptr; // [pairs][32]
 };
 
 namespace hlq {
@@ -82,6 +89,11 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
                      const hlq_input_op *op = nullptr);
 int launch_lut4_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, void *y, int y_dtype,
                      void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// The extra bit-plane of a weight that has one (hlq_sparse.cu): into fp32 accumulators [m][acc_stride] when
+// `acc` is given, else added to y in place.  No-op for weights without the plane.
+int launch_sparse_plane(const hlq_weight *w, int m, const void *x, int x_dtype, float *acc, int acc_stride, void *y,
+                        int y_dtype, cudaStream_t stream);
+void free_sparse(hlq_weight *w);
 // Splits of the context per kv head the attention kernel uses for a cache of max_ctx positions.
 int attention_splits(int head_kv, int max_ctx);
 int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, void *y,

@@ -9,7 +9,16 @@ loader (C++/ops/src/arm/parameters.cpp:5-70), per linear directory:
     bias.bin (optional)  fp16  [N]
     weight_config.json   weight_data_len, base_bit, use_sparse, in_channel, out_channel,
                          has_bias (+ groupsize, which the reference's loader reads but its
-                         exporter does not write)
+                         exporter does not write; + sparse_mask_len with use_sparse)
+
+With ``use_sparse`` the runtime's loader (parameters.cpp:44-64) expects one EXTRA bit-plane
+for a list of 32-row x g-channel blocks: ``weight_mask.bin`` holds uint32 pairs (first output
+row of the block, first input channel of its group), ``sparse_mask_len`` counts the uint32s;
+``w_quant.bin`` continues, after the q dense planes, with one [32][g/8] byte block per pair
+(arm_t_mac_kernal.cpp:577-588) and ``w_scale.bin`` with 32 fp16 scales per pair
+(parameters.cpp:45, arm_t_mac_kernal.cpp:761-764):
+    w[x + r, y + c] += scale[pair][r] * bit[pair][r][c]      (arm_t_mac_kernal.cpp:678-788).
+No exporter in the reference writes this (HLQ.py:180 hard-codes use_sparse = False).
 
 Packing goes through the C ABI (hlq_pack_bits / hlq_unpack_bits); there is no NumPy
 re-implementation here.
@@ -27,6 +36,18 @@ from . import _lib
 
 
 @dataclass
+class SparsePlane:
+    """The optional extra bit-plane of an exported linear: P blocks of 32 rows x g channels."""
+    mask: np.ndarray               # uint32 [P, 2]: (first output row, first input channel), sorted by row
+    blocks: np.ndarray             # uint8  [P, 32, g/8]: bit j of byte i = channel 8i+j of the group
+    scales: np.ndarray             # fp16   [P, 32]: one scale per row of the block
+
+    @property
+    def pairs(self) -> int:
+        return int(self.mask.shape[0])
+
+
+@dataclass
 class ExportedLinear:
     """The arrays of one exported linear, as NumPy views of the files' bytes."""
     w_quant: np.ndarray            # uint8 [q, N, K/8]
@@ -34,6 +55,7 @@ class ExportedLinear:
     w_zero: np.ndarray             # fp16  [N, K/g]
     bias: Optional[np.ndarray]     # fp16  [N] or None
     groupsize: int
+    sparse: Optional[SparsePlane] = None
 
     @property
     def bits(self) -> int:
@@ -113,18 +135,30 @@ def write_export_dir(path: str, lin: ExportedLinear, write_groupsize: bool = Fal
     """
     os.makedirs(path, exist_ok=True)
     lin.w_zero.astype(np.float16).tofile(os.path.join(path, "w_zero.bin"))
-    lin.w_scale.astype(np.float16).tofile(os.path.join(path, "w_scale.bin"))
-    lin.w_quant.astype(np.uint8).tofile(os.path.join(path, "w_quant.bin"))
+    sp = lin.sparse
+    with open(os.path.join(path, "w_scale.bin"), "wb") as f:
+        f.write(np.ascontiguousarray(lin.w_scale, dtype=np.float16).tobytes())
+        if sp is not None:
+            f.write(np.ascontiguousarray(sp.scales, dtype=np.float16).tobytes())
+    with open(os.path.join(path, "w_quant.bin"), "wb") as f:
+        f.write(np.ascontiguousarray(lin.w_quant, dtype=np.uint8).tobytes())
+        if sp is not None:
+            f.write(np.ascontiguousarray(sp.blocks, dtype=np.uint8).tobytes())
+    dense_len = int(lin.in_channel * lin.out_channel * lin.bits / 8)
     cfg = {
-        "weight_data_len": int(lin.in_channel * lin.out_channel * lin.bits / 8),
+        "weight_data_len": dense_len + (0 if sp is None else int(sp.blocks.size)),
         "base_bit": int(lin.bits),
-        "use_sparse": False,
+        "use_sparse": sp is not None,
         "in_channel": int(lin.in_channel),
         "out_channel": int(lin.out_channel),
         "has_bias": lin.bias is not None,
     }
     if lin.bias is not None:
         lin.bias.astype(np.float16).tofile(os.path.join(path, "bias.bin"))
+    if sp is not None:
+        cfg["sparse_mask_len"] = int(sp.mask.size)
+        cfg["groupsize"] = int(lin.groupsize)        # the block size cannot be derived without it
+        np.ascontiguousarray(sp.mask, dtype=np.uint32).tofile(os.path.join(path, "weight_mask.bin"))
     if write_groupsize:
         cfg["groupsize"] = int(lin.groupsize)
     with open(os.path.join(path, "weight_config.json"), "w") as f:
@@ -136,9 +170,10 @@ def read_export_dir(path: str) -> ExportedLinear:
 
     Errors follow the reference's loader where it has any: a missing or invalid
     ``weight_config.json`` raises (fileutils.cpp:32-43).  Unlike the reference, short
-    reads raise too instead of being ignored (parameters.cpp:38), and sparse exports are
-    rejected.  The group size is taken from the config when present, else derived from
-    the size of ``w_zero.bin``.
+    reads raise too instead of being ignored (parameters.cpp:38).  The group size is taken
+    from the config when present, else derived from the size of ``w_zero.bin``.  With
+    ``use_sparse`` the extra plane's blocks, scales and mask are read as the loader does
+    (parameters.cpp:44-64).
     """
     cfg_path = os.path.join(path, "weight_config.json")
     if not os.path.exists(cfg_path):
@@ -148,15 +183,15 @@ def read_export_dir(path: str) -> ExportedLinear:
             cfg = json.load(f)
         except json.JSONDecodeError as e:
             raise RuntimeError(f"Invalid json file: {cfg_path}") from e
-    if cfg.get("use_sparse", False):
-        raise NotImplementedError("sparse extra-bit planes are not supported")
+    use_sparse = bool(cfg.get("use_sparse", False))
     q = int(cfg["base_bit"])
     k = int(cfg["in_channel"])
     n = int(cfg["out_channel"])
     if q < 1 or q > 4 or k % 8 or n <= 0:
         raise ValueError(f"unsupported weight_config: bits={q} in={k} out={n}")
-    want = int(cfg.get("weight_data_len", n * k * q // 8))
-    if want != n * k * q // 8:
+    dense = n * k * q // 8
+    want = int(cfg.get("weight_data_len", dense))
+    if not use_sparse and want != dense:
         raise ValueError("weight_data_len does not match in_channel*out_channel*base_bit/8")
     w_quant = np.fromfile(os.path.join(path, "w_quant.bin"), dtype=np.uint8)
     if w_quant.size != want:
@@ -170,7 +205,27 @@ def read_export_dir(path: str) -> ExportedLinear:
     if k % g or g % 8 or w_zero.size != n * k // g:
         raise ValueError(f"w_zero.bin holds {w_zero.size} values, expected {n * k // g} at g={g}")
     w_scale = np.fromfile(os.path.join(path, "w_scale.bin"), dtype=np.float16)
-    if w_scale.size != q * n * k // g:
+    sparse = None
+    if use_sparse:
+        mlen = int(cfg.get("sparse_mask_len", -1))
+        if mlen < 0 or mlen % 2:
+            raise ValueError("use_sparse needs an even sparse_mask_len")
+        pairs = mlen // 2
+        mask = np.fromfile(os.path.join(path, "weight_mask.bin"), dtype=np.uint32)
+        if mask.size != mlen:
+            raise ValueError(f"weight_mask.bin holds {mask.size} values, expected {mlen}")
+        if w_quant.size != dense + pairs * 4 * g:
+            raise ValueError(f"w_quant.bin holds {w_quant.size} bytes, expected {dense + pairs * 4 * g} with {pairs} blocks")
+        if w_scale.size != q * n * k // g + pairs * 32:
+            raise ValueError(f"w_scale.bin holds {w_scale.size} values, expected {q * n * k // g + pairs * 32}")
+        mask = mask.reshape(pairs, 2)
+        if pairs and (np.any(mask[:, 0] % 32) or np.any(mask[:, 1] % g) or mask[:, 0].max() + 32 > n
+                      or mask[:, 1].max() + g > k):
+            raise ValueError("weight_mask.bin names a block outside the weight or off the 32-row / group grid")
+        sparse = SparsePlane(mask, w_quant[dense:].reshape(pairs, 32, g // 8),
+                             w_scale[q * n * k // g:].reshape(pairs, 32))
+        w_quant, w_scale = w_quant[:dense], w_scale[:q * n * k // g]
+    elif w_scale.size != q * n * k // g:
         raise ValueError(f"w_scale.bin holds {w_scale.size} values, expected {q * n * k // g}")
     bias = None
     if cfg.get("has_bias", False):
@@ -178,7 +233,7 @@ def read_export_dir(path: str) -> ExportedLinear:
         if bias.size != n:
             raise ValueError(f"bias.bin holds {bias.size} values, expected {n}")
     return ExportedLinear(w_quant.reshape(q, n, k // 8), w_scale.reshape(q, n, k // g),
-                          w_zero.reshape(n, k // g), bias, g)
+                          w_zero.reshape(n, k // g), bias, g, sparse)
 
 
 def repack_host(lin: ExportedLinear):

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .format import ExportedLinear, export_from_tensors, read_export_dir
+from .format import ExportedLinear, SparsePlane, export_from_tensors, read_export_dir
 
 _DTYPES = {torch.float16: _lib.HLQ_F16, torch.bfloat16: _lib.HLQ_BF16, torch.float32: _lib.HLQ_F32}
 
@@ -59,7 +59,22 @@ class HLQWeight:
                 _src_ptr(keep[3]), lin.in_channel, lin.out_channel, lin.groupsize, lin.bits,
                 dev.index, tp_rank, tp_size, shard_mode, flags, _stream_ptr(dev))
         _lib.check(st, "hlq_weight_from_export")
-        return cls(out.value)
+        self = cls(out.value)
+        if lin.sparse is not None and lin.sparse.pairs:
+            sp = lin.sparse
+            mask = np.ascontiguousarray(sp.mask, dtype=np.uint32)
+            blocks = np.ascontiguousarray(sp.blocks, dtype=np.uint8)
+            scales = np.ascontiguousarray(sp.scales, dtype=np.float16)
+            with torch.cuda.device(dev):
+                _lib.check(_lib.lib().hlq_weight_set_sparse(self._h, mask.ctypes.data, sp.pairs, blocks.ctypes.data,
+                                                            scales.ctypes.data, _stream_ptr(dev)),
+                           "hlq_weight_set_sparse")
+        return self
+
+    def sparse_pairs(self) -> int:
+        v = ctypes.c_int(0)
+        _lib.check(_lib.lib().hlq_weight_sparse_pairs(self.handle, ctypes.byref(v)), "hlq_weight_sparse_pairs")
+        return v.value
 
     @classmethod
     def alloc(cls, in_channel, out_channel, groupsize, bits, has_bias=False, device=0, flags=0):
@@ -102,7 +117,18 @@ class HLQWeight:
                 self.handle, wq.ctypes.data, ws.ctypes.data, wz.ctypes.data,
                 None if bias is None else bias.ctypes.data, _stream_ptr(self.device))
         _lib.check(st, "hlq_weight_to_export")
-        return ExportedLinear(wq, ws, wz, bias, g)
+        sparse = None
+        pairs = self.sparse_pairs()
+        if pairs:
+            mask = np.empty((pairs, 2), np.uint32)
+            blocks = np.empty((pairs, 32, g // 8), np.uint8)
+            scales = np.empty((pairs, 32), np.float16)
+            with torch.cuda.device(self.device):
+                _lib.check(_lib.lib().hlq_weight_get_sparse(self.handle, mask.ctypes.data, blocks.ctypes.data,
+                                                            scales.ctypes.data, _stream_ptr(self.device)),
+                           "hlq_weight_get_sparse")
+            sparse = SparsePlane(mask, blocks, scales)
+        return ExportedLinear(wq, ws, wz, bias, g, sparse)
 
     def free(self):
         if self._h is not None:

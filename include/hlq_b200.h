@@ -158,6 +158,25 @@ int hlq_weight_buffers(const hlq_weight *w, void **d_planes, int64_t *planes_byt
 int hlq_weight_alloc(hlq_weight **out, int in_ch, int out_ch, int groupsize, int bits,
                      int has_bias, int device, unsigned flags);
 
+/* The runtime's optional extra bit-plane ("sparse" weights, weight_config.json use_sparse = true): for a
+ * list of blocks of 32 output rows x one group of input channels, one more bit-plane with one fp16 scale per
+ * row, w[x + r, y + c] += scale[pair][r] * bit[pair][r][c].  h_mask: uint32 [pairs][2] = (first output row of
+ * the block, first input channel of its group) in coordinates of the FULL weight; h_blocks: uint8
+ * [pairs][32][g/8] (bit j of byte i = channel 8i+j of the group); h_scales: fp16 [pairs][32].  A sharded handle
+ * keeps the blocks of its shard.  hlq_linear_forward then includes the plane (exactly for the LUT GEMV, which
+ * takes it into its fp32 accumulators; as an addition to y after the other kernels); the grouped, fused
+ * all-reduce, static-scratch and chain entry points refuse such weights (HLQ_ERR_UNSUPPORTED).
+ * hlq_weight_get_sparse returns the kept blocks in the shard's coordinates (buffers sized by
+ * hlq_weight_sparse_pairs).  Synchronize `stream`.
+ * Replaces: the use_sparse branch of load_Parameter (C++/ops/src/arm/parameters.cpp:44-64), the re-layout
+ * t_mac_g4_rearrange_weight_sparse_impl (C++/ops/src/arm/arm_t_mac_kernal.cpp:554-646) and the kernel
+ * t_mac_g4_float_update_sparse_impl (arm_t_mac_kernal.cpp:678-788) with its drivers (arm_gemm.cpp:390-563). */
+int hlq_weight_set_sparse(hlq_weight *w, const uint32_t *h_mask, int pairs, const uint8_t *h_blocks,
+                          const uint16_t *h_scales, void *stream);
+int hlq_weight_sparse_pairs(const hlq_weight *w, int *pairs);
+int hlq_weight_get_sparse(const hlq_weight *w, uint32_t *h_mask, uint8_t *h_blocks, uint16_t *h_scales,
+                          void *stream);
+
 /* ---- forward ------------------------------------------------------------------------ */
 
 /* Bytes of device scratch hlq_linear_forward needs for this problem (0 is possible).

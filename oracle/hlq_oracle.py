@@ -164,13 +164,32 @@ def dequantize_export(w_quant, w_scale16, w_zero16, g: int, dtype=np.float64) ->
     return (bits * alpha_full).sum(axis=0) + np.repeat(z, g, axis=1)
 
 
-def hlq_linear(x, w_quant, w_scale16, w_zero16, g: int, bias16=None, dtype=np.float64):
+def add_sparse_plane(w, mask, blocks, scales16, g: int):
+    """The runtime's optional extra bit-plane added to a dequantized weight ``w`` [N, K]:
+    for every listed block (x = first row, y = first channel of a group)
+    ``w[x + r, y + c] += scale[r] * bit[r][c]``, which is what the reference's kernel adds to
+    its output through its tables (C++/ops/src/arm/arm_t_mac_kernal.cpp:678-788; block and
+    scale order as re-laid-out at :577-588 and read at :761-764; loader
+    C++/ops/src/arm/parameters.cpp:44-64).  Bits are LSB-first along the channels, as in
+    the dense planes."""
+    mask = np.asarray(mask).reshape(-1, 2)
+    for p in range(mask.shape[0]):
+        x0, y0 = int(mask[p, 0]), int(mask[p, 1])
+        bits = np.unpackbits(np.asarray(blocks[p], dtype=np.uint8), axis=1, bitorder="little")[:, :g]
+        w[x0:x0 + 32, y0:y0 + g] += np.asarray(scales16[p]).astype(w.dtype)[:, None] * bits.astype(w.dtype)
+    return w
+
+
+def hlq_linear(x, w_quant, w_scale16, w_zero16, g: int, bias16=None, dtype=np.float64, sparse=None):
     """Value oracle: ``y = x . W_hat^T (+ bias)`` in ``dtype`` (default fp64).
 
     This is the reference's HLQ matmul in the form its evaluation uses: the
-    dequantized weight written into an ``nn.Linear`` (HLQ.py:173).
+    dequantized weight written into an ``nn.Linear`` (HLQ.py:173).  ``sparse``: optional
+    (mask, blocks, scales) of the runtime's extra bit-plane (see add_sparse_plane).
     """
     w = dequantize_export(w_quant, w_scale16, w_zero16, g, dtype)
+    if sparse is not None:
+        add_sparse_plane(w, sparse[0], sparse[1], sparse[2], g)
     y = np.asarray(x).astype(dtype) @ w.T
     if bias16 is not None:
         y = y + np.asarray(bias16).astype(dtype)[None, :]
