@@ -41,36 +41,48 @@ __global__ void __launch_bounds__(kSparseWarps * 32) sparse_plane_kernel(const S
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p = blockIdx.x * kSparseWarps + warp;
     if (p >= a.pairs) return;
-    const int x0 = (int)a.mask[2 * p], y0 = (int)a.mask[2 * p + 1];
+    // A warp takes a whole run of consecutive pairs with the same first row (the list is sorted by
+    // rows, parameters.cpp hands it over that way and the reference's kernel relies on it too,
+    // arm_t_mac_kernal.cpp:766-785): their sums meet in a register and the output row is touched
+    // once.  Pairs in the middle of a run are left to the warp of the run's first pair; the final
+    // additions are atomic, so an unsorted list costs precision of 16-bit outputs, not correctness.
+    const int x0 = (int)a.mask[2 * p];
+    if (p > 0 && (int)a.mask[2 * (p - 1)] == x0) return;
+    int pend = p + 1;
+    while (pend < a.pairs && (int)a.mask[2 * pend] == x0) ++pend;
     const int gb = a.g / 8;
-    const uint8_t *bits = a.blocks + ((size_t)p * 32 + lane) * gb;
-    const float scale = __half2float(__ushort_as_half(a.scales[(size_t)p * 32 + lane]));
     const int row = x0 + lane;
     for (int mi = 0; mi < a.m; ++mi) {
-        const uint16_t *xr = (const uint16_t *)a.x + (size_t)mi * a.k + y0;
-        for (int c = lane; c < a.g; c += 32)
-            xs[warp][c] = a.x_dtype == HLQ_BF16 ? __uint_as_float((uint32_t)xr[c] << 16)
-                                                : __half2float(__ushort_as_half(xr[c]));
-        __syncwarp();
-        float s = 0.f;
-        for (int i = 0; i < gb; ++i) {
-            const unsigned b = bits[i];
+        float total = 0.f;
+        for (int pp = p; pp < pend; ++pp) {
+            const int y0 = (int)a.mask[2 * pp + 1];
+            const uint8_t *bits = a.blocks + ((size_t)pp * 32 + lane) * gb;
+            const float scale = __half2float(__ushort_as_half(a.scales[(size_t)pp * 32 + lane]));
+            const uint16_t *xr = (const uint16_t *)a.x + (size_t)mi * a.k + y0;
+            for (int c = lane; c < a.g; c += 32)
+                xs[warp][c] = a.x_dtype == HLQ_BF16 ? __uint_as_float((uint32_t)xr[c] << 16)
+                                                    : __half2float(__ushort_as_half(xr[c]));
+            __syncwarp();
+            float s = 0.f;
+            for (int i = 0; i < gb; ++i) {
+                const unsigned b = bits[i];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if ((b >> j) & 1u) s += xs[warp][8 * i + j];
+                for (int j = 0; j < 8; ++j)
+                    if ((b >> j) & 1u) s += xs[warp][8 * i + j];
+            }
+            total += s * scale;
+            __syncwarp();
         }
-        s *= scale;
         if (row < a.n) {
             if (a.acc) {
-                atomicAdd(a.acc + (size_t)mi * a.acc_stride + row, s);
+                atomicAdd(a.acc + (size_t)mi * a.acc_stride + row, total);
             } else {
                 const size_t idx = (size_t)mi * a.n + row;
-                if (a.y_dtype == HLQ_F32) ((float *)a.y)[idx] += s;
-                else if (a.y_dtype == HLQ_F16) ((__half *)a.y)[idx] = __float2half_rn(__half2float(((__half *)a.y)[idx]) + s);
-                else ((__nv_bfloat16 *)a.y)[idx] = __float2bfloat16_rn(__bfloat162float(((__nv_bfloat16 *)a.y)[idx]) + s);
+                if (a.y_dtype == HLQ_F32) atomicAdd((float *)a.y + idx, total);
+                else if (a.y_dtype == HLQ_F16) atomicAdd((__half *)a.y + idx, __float2half_rn(total));
+                else atomicAdd((__nv_bfloat16 *)a.y + idx, __float2bfloat16_rn(total));
             }
         }
-        __syncwarp();
     }
 }
 
