@@ -43,6 +43,7 @@ class WeightInfo(ctypes.Structure):
 # name -> (restype, argtypes); every symbol include/hlq_b200.h declares
 SIGNATURES = {
     "hlq_quantize_with_scales_device": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int, c_void_p]),
+    "hlq_fit_alternating_device": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int, c_int, c_void_p]),
     "hlq_pack_bits": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64]),
     "hlq_unpack_bits": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64]),
     "hlq_pack_bits_device": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p]),

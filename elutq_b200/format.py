@@ -289,3 +289,40 @@ def quantize_with_scales_device(w, scales, zeros):
                                                         torch.cuda.current_stream(w.device).cuda_stream)
     _lib.check(st, "hlq_quantize_with_scales_device")
     return out
+
+
+def fit_alternating_device(w, bits: int, iters: int = 10):
+    """Scales and offset of every block of weights by the reference's alternating fit
+    (find_optimal_params_alternating, quant.py:118-153) on the GPU.
+
+    ``w`` fp32 CUDA ``[blocks, g]`` -> (scales fp32 ``[blocks, bits]``, zeros fp32 ``[blocks]``)."""
+    import torch
+    from . import _lib
+    if not w.is_cuda:
+        raise RuntimeError("fit_alternating_device runs on CUDA tensors only")
+    w = w.contiguous().float()
+    blocks, g = w.shape
+    scales = torch.empty((blocks, bits), dtype=torch.float32, device=w.device)
+    zeros = torch.empty((blocks,), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        st = _lib.lib().hlq_fit_alternating_device(w.data_ptr(), scales.data_ptr(), zeros.data_ptr(), blocks, g, bits,
+                                                   iters, torch.cuda.current_stream(w.device).cuda_stream)
+    _lib.check(st, "hlq_fit_alternating_device")
+    return scales, zeros
+
+
+def pseudo_quantize_device(w, bits: int, groupsize: int, iters: int = 10):
+    """What the reference's ``pseudo_quantize_tensor(w, n_bit, True, g, False, get_scale_zp=True,
+    use_alternating_optimization=True)`` returns (quant.py:185-213), computed on the GPU:
+    (reconstruction fp32 ``[N, K]``, quantized_w uint8 ``[N, K, q]``, w_scale fp32 ``[N, K/g, q]``,
+    w_zero fp32 ``[N, K/g, 1]``) - the tensors ``HLQ.export`` takes (HLQ.py:207-208) and
+    ``export_from_tensors`` turns into the exported arrays."""
+    n, k = w.shape
+    if k % groupsize:
+        raise ValueError("in_channel must be a multiple of the group size")
+    blocks = w.contiguous().float().reshape(-1, groupsize)
+    scales, zeros = fit_alternating_device(blocks, bits, iters)
+    quantized = quantize_with_scales_device(blocks, scales, zeros)
+    recon = (quantized.float() * scales.unsqueeze(1)).sum(dim=2) + zeros.unsqueeze(1)
+    return (recon.reshape(n, k), quantized.reshape(n, k, bits), scales.reshape(n, k // groupsize, bits),
+            zeros.reshape(n, k // groupsize, 1))

@@ -87,6 +87,18 @@ typedef struct hlq_weight_info {
 int hlq_quantize_with_scales_device(const float *d_w, const float *d_scales, const float *d_zeros,
                                     uint8_t *d_out, int64_t blocks, int g, int q, void *stream);
 
+/* The fit that precedes the assignment: for every block of g weights (fp32 [blocks][g]) the q plane scales
+ * and the offset that minimize the squared error, found by alternating `iters` times (the reference uses
+ * 10) between assigning every weight to the nearest of the 2^q values and solving the (q+1) x (q+1) normal
+ * equations for scales and offset (pseudo-inverse: a plane that no weight uses gets scale 0).  Start: plane j
+ * = range / (2^q - 1) * 2^j, offset = minimum.  scales fp32 [blocks][q], zeros fp32 [blocks]; g <= 1024.
+ * hlq_fit_alternating_device + hlq_quantize_with_scales_device + hlq_pack_bits_device produce, on the device,
+ * what the reference's pseudo_quantize_tensor(use_alternating_optimization=True) and its exporter produce.
+ * Replaces: find_optimal_params_alternating, GPTQ/quant.py:118-153, with optimize_s_batch_with_constant,
+ * GPTQ/quant.py:104-116. */
+int hlq_fit_alternating_device(const float *d_w, float *d_scales, float *d_zeros, int64_t blocks, int g, int q,
+                               int iters, void *stream);
+
 /* ---- bit-plane packing -------------------------------------------------------------- */
 
 /* bits: uint8 [q][n][k] of 0/1  ->  packed: uint8 [q][n][k/8]; channel 8i+j goes to bit j

@@ -164,6 +164,31 @@ def dequantize_export(w_quant, w_scale16, w_zero16, g: int, dtype=np.float64) ->
     return (bits * alpha_full).sum(axis=0) + np.repeat(z, g, axis=1)
 
 
+def fit_alternating(t, bits: int, iters: int = 10):
+    """The reference's alternating fit of plane scales and offset per block, restated in NumPy
+    float32 (GPTQ/quant.py:118-153 with :95-102 and :104-116): start from range / (2^q - 1) * 2^j
+    and the minimum; `iters` times assign every weight to the nearest of the 2^q values (first
+    minimum; value i has bit j = (i >> j) & 1, then the constant) and solve the (q+1) x (q+1)
+    normal equations with a pseudo-inverse.  Returns (scales [blocks, q], zeros [blocks])."""
+    t = np.asarray(t, dtype=np.float32)
+    nb, g = t.shape
+    lo, hi = t.min(axis=1), t.max(axis=1)
+    step = (hi - lo) / np.float32(2 ** bits - 1)
+    scales = np.concatenate([step[:, None] * (2.0 ** np.arange(bits, dtype=np.float32))[None, :], lo[:, None]],
+                            axis=1).astype(np.float32)
+    combos = np.array([[(i >> j) & 1 for j in range(bits)] + [1] for i in range(2 ** bits)], dtype=np.float32)
+    rtol = (bits + 1) * np.finfo(np.float32).eps          # torch.linalg.pinv's default for float32
+    for _ in range(iters):
+        comb_vals = scales @ combos.T                                              # [nb, 2^q]
+        idx = np.argmin(np.abs(t[:, :, None] - comb_vals[:, None, :]), axis=2)     # [nb, g]
+        B = combos[idx]                                                            # [nb, g, q+1]
+        BtB = np.einsum("bgi,bgj->bij", B, B)
+        BtY = np.einsum("bgi,bg->bi", B, t)
+        inv = np.stack([np.linalg.pinv(m, rcond=rtol) for m in BtB]).astype(np.float32)
+        scales = np.einsum("bij,bj->bi", inv, BtY).astype(np.float32)
+    return scales[:, :bits], scales[:, bits]
+
+
 def add_sparse_plane(w, mask, blocks, scales16, g: int):
     """The runtime's optional extra bit-plane added to a dequantized weight ``w`` [N, K]:
     for every listed block (x = first row, y = first channel of a group)
