@@ -261,10 +261,14 @@ def decode_config(model, cfg, world, kind):
             "path": kind}
 
 
-DECODE_PATH = ("own kernels only: residual+RMSNorm, q/k/v and gate/up as grouped LUT GEMVs, RoPE + KV append + "
-               "attention in one kernel, gated SiLU, o/down LUT GEMVs with the all-reduce fused into the kernel "
-               "(peer stores over NVLink) at N > 1, w4g128 lm_head, argmax; one CUDA graph per step; NCCL only for "
-               "the all-gather of the arg-max")
+DECODE_PATH = ("own kernels only: all layers of a token in ONE persistent kernel (decode chain: per layer the stages "
+               "q|k|v LUT GEMV, RoPE + KV append + attention, o, gate/up, down; RMSNorm in the table build, residual "
+               "adds and gated SiLU in the completion pass, the rank sums of o and down inside the kernel by peer "
+               "stores over NVLink at N > 1), then final norm, w4g128 lm_head, argmax; one CUDA graph per step; "
+               "NCCL only for the all-gather of the arg-max")
+PER_OP_PATH = ("own kernels only, one launch per op (8 per layer): residual+RMSNorm, q/k/v and gate/up as grouped LUT "
+               "GEMVs, RoPE + KV append + attention in one kernel, gated SiLU, o/down LUT GEMVs with the all-reduce "
+               "fused into the kernel at N > 1, w4g128 lm_head, argmax; one CUDA graph per step")
 
 
 def run_reference(args):
@@ -677,7 +681,8 @@ def run_decode(args):
         "dtype": "f32 accumulate over fp16 activations, 1-bit planes; fp16 between the ops",
         "data": "synthetic",
         "config": decode_config(args.model, cfg, world,
-                                DECODE_PATH if not args.torch_glue else "PyTorch glue ops (parity reference)"),
+                                "PyTorch glue ops (parity reference)" if args.torch_glue else
+                                (DECODE_PATH if dec.use_chain else PER_OP_PATH)),
         "e2e": {"value": 1.0 / sec_e2e, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
         "gpu_launches": int(launches * args.steps * REPEATS),
         "launches_per_step": int(launches),
@@ -688,7 +693,8 @@ def run_decode(args):
                      "frac": my_bytes / sec / 1e9 / peaks["hbm"],
                      "traffic": NCU_TRAFFIC_RATIO * my_bytes / gemv_launches,
                      "traffic_source": "ncu capture of a 2-layer launch of the kernel, scaled by algorithmic bytes",
-                     "peak_source": f"of {peaks['kind']}", "kernel": "lut8_gemv_kernel",
+                     "peak_source": f"of {peaks['kind']}",
+                     "kernel": "decode_chain_kernel" if dec.use_chain else "lut8_gemv_kernel",
                      "launches_per_step": gemv_launches,
                      "note": "achieved = this rank's linear bytes per token over the WHOLE step time (norms, "
                              "attention, collectives and launch gaps included), a lower bound of the kernel's own "

@@ -10,7 +10,7 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("HLQ_B200_LIB") or os.path.join(HERE, "csrc", "libhlq_b200.so")
+LIB_PATH = os.path.join(HERE, "csrc", "libhlq_b200.so")
 
 HLQ_OK = 0
 HLQ_F16, HLQ_BF16, HLQ_F32 = 0, 1, 2

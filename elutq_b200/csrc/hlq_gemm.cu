@@ -496,10 +496,6 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, w->device);
     int rows = 128, tile_m = 256;
     choose_tiles(w->n, m, sms, &rows, &tile_m);
-    static const int force_rows = getenv("HLQ_GEMM_ROWS") ? atoi(getenv("HLQ_GEMM_ROWS")) : 0;
-    static const int force_tm = getenv("HLQ_GEMM_TM") ? atoi(getenv("HLQ_GEMM_TM")) : 0;
-    if (force_rows == 128 || force_rows == 256) rows = force_rows;
-    if (force_tm >= 32 && force_tm <= 256 && force_tm % 32 == 0) tile_m = force_tm;
 
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {(cuuint64_t)w->k, (cuuint64_t)m};

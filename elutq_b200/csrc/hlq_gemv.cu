@@ -146,10 +146,7 @@ static_assert(kAuxGamma + 2048 <= kAuxBytes, "aux area");
 // the restart of the load ring): CTAs that get many short slices would otherwise finish last.
 // Only launches of several jobs need it (a single job's slices are all alike); there
 // GemvArgs::seg_cost = kSegCost, else 0.
-#ifndef HLQ_SEG_COST
-#define HLQ_SEG_COST 40
-#endif
-constexpr int kSegCost = HLQ_SEG_COST;
+constexpr int kSegCost = 40;
 __host__ __device__ static inline long long launch_units(int slices, int duos, int seg_cost) {
     return (long long)slices * (duos + seg_cost);
 }
@@ -951,23 +948,18 @@ static int launch_lut8_rows(int q, int gpw, const GemvArgs &a, dim3 grid, cudaSt
     return HLQ_ERR_SHAPE;
 }
 
-static int env_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
 
 // grid.y = rows of x.  Two or more rows go through passes of two rows each (half2 table
 // entries: one lookup serves both) plus a single-row pass for an odd last row.  The table
 // entries of such a pass are rounded to fp16 (2^-11, as the reference's tables are), which is
 // below the rounding of a 16-bit output; fp32 outputs therefore keep one row per pass and
-// fp32 entries, and so do the fused all-reduce and HLQ_GEMV_PAIR_ROWS=0.
+// fp32 entries, and so does the fused all-reduce.
 static int launch_lut8_any(int q, int gpw, const GemvArgs &a_in, dim3 grid, cudaStream_t stream) {
-    static const int pair_rows = env_int("HLQ_GEMV_PAIR_ROWS", 1);
     const int m = (int)grid.y;
     GemvArgs a = a_in;
     a.row_base = 0;
     if (a.one_row_passes) return launch_lut8_rows<1, true>(q, gpw, a, grid, stream);
-    if (m < 2 || a.tp || a.y_is_f32 || !pair_rows) return launch_lut8_rows<1, false>(q, gpw, a, grid, stream);
+    if (m < 2 || a.tp || a.y_is_f32) return launch_lut8_rows<1, false>(q, gpw, a, grid, stream);
     int rc = launch_lut8_rows<2, false>(q, gpw, a, dim3(grid.x, m / 2), stream);
     if (rc || !(m & 1)) return rc;
     a.row_base = m - 1;
@@ -1029,7 +1021,6 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
     if (rc) return rc;
     if ((uint32_t)di->max_dyn_smem < kLut8DynSmem) return HLQ_ERR_NO_DEVICE;
 
-    static const int force_ctas = env_int("HLQ_GEMV_CTAS", 0);
     const size_t xsz = 2, ysz = y_dtype == HLQ_F32 ? 4 : 2;
     for (int m0 = 0; m0 < m; m0 += kLutMaxM) {
         const int mc = (m - m0) < kLutMaxM ? (m - m0) : kLutMaxM;
@@ -1047,7 +1038,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         rc = apply_input_op(a.single, op, x_dtype, m0);
         if (rc) return rc;
         a.one_row_passes = a.single.xop != HLQ_INPUT_PLAIN;
-        int ctas = force_ctas > 0 ? force_ctas : di->sms;
+        int ctas = di->sms;
         if ((long long)d.slices * d.duos < ctas) ctas = d.slices * d.duos;
         // a weight with the extra bit-plane: its blocks' sums go into the accumulators first
         rc = launch_sparse_plane(w, mc, a.single.x, x_dtype, ws.partial, d.np, nullptr, y_dtype, stream);
@@ -1465,7 +1456,6 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     int rc = device_info(g->device, &di);
     if (rc) return rc;
     if ((uint32_t)di->max_dyn_smem < kLut8DynSmem) return HLQ_ERR_NO_DEVICE;
-    static const int force_ctas = env_int("HLQ_GEMV_CTAS", 0);
     GemvArgs a = {};
     a.jobs = g->d_jobs;
     a.njobs = g->count;
@@ -1476,7 +1466,7 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.spin_limit = kDefaultSpinLimit;
     a.y_is_f32 = g->jobs_host[0].y_dtype == HLQ_F32;
     a.one_row_passes = g->one_row_passes;
-    int ctas = force_ctas > 0 ? force_ctas : di->sms;
+    int ctas = di->sms;
     if (g->duo_units < ctas) ctas = (int)g->duo_units;
     return launch_lut8_any(g->q, g->gpw, a, dim3(ctas, m), (cudaStream_t)stream);
 }
