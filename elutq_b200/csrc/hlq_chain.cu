@@ -220,11 +220,17 @@ __device__ __noinline__ bool chain_attention(const AttnArgs *args, int hk, int s
 // The consumers' loop over SEGMENT / NOTHING items, from item `i` on, until the next item is an
 // ATTENTION item (true; `i` is its index) or the END (false).
 template <int Q, int GPW>
-__device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned char *aux, uint32_t aux_u32, uint32_t tbl,
-                                                 ChainItem *ring, volatile int *fail, unsigned long long budget_long,
-                                                 int *decide, const float *inv_rms_s, float *xsum, int &i) {
+__device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned char *aux, uint32_t tbl, int &i) {
+    // everything else is re-derived from `aux` where it is needed: the fewer values stay live across
+    // the streaming loop, the fewer of its registers get spilled
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t mb_desc = aux_u32 + kChAuxMbarDesc, mb_x = aux_u32 + kChAuxMbarX;
+#define CH_AUX_U32 (smem_u32(aux))
+#define CH_MB_DESC (CH_AUX_U32 + kChAuxMbarDesc)
+#define CH_MB_X (CH_AUX_U32 + kChAuxMbarX)
+#define CH_RING ((ChainItem *)(aux + kChAuxItem))
+#define CH_FAIL ((volatile int *)(aux + kChAuxFlag))
+#define CH_DECIDE ((int *)(aux + kChAuxDecide))
+#define CH_BUDGET_LONG (budget_ns(a.spin_limit) << 3)
     auto stamp = [&](int it, int k) {
         if (a.trace && it < a.trace_items) a.trace[((size_t)blockIdx.x * a.trace_items + it) * 16 + k] = global_ns();
     };
@@ -260,23 +266,23 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
         if (kRing == 3 && d + kChConsumerWarps < dend)
             load_tile<Q, GPW>(t1, pl + kChConsumerWarps * kDuoPlaneBytes, mp + kChConsumerWarps * kDuoMetaElems);
     };
-    open_item(ring[i & 1]);
+    open_item(CH_RING[i & 1]);
     for (;; ++i) {
         const int slot = i & 1;
         if (tid == 0) stamp(i, 2);
-        const bool got = mbar_wait_timed(mb_x + 8 * slot, (i >> 1) & 1, fail, budget_long);
+        const bool got = mbar_wait_timed(CH_MB_X + 8 * slot, (i >> 1) & 1, CH_FAIL, CH_BUDGET_LONG);
         if (tid == 0) stamp(i, 3);
         // one thread decides for all whether the item runs (the failure flag can be raised at
         // any moment by another role; the barriers below need one answer)
-        if (tid == 0) decide[slot] = (got && !*fail) ? 1 : 0;
+        if (tid == 0) CH_DECIDE[slot] = (got && !*CH_FAIL) ? 1 : 0;
         named_bar_sync<kChBarConsumers, kChConsumers>();     // also: everyone is done with the old table
-        const bool run = decide[slot] != 0;
+        const bool run = CH_DECIDE[slot] != 0;
         if (tid == 0) stamp(i, 4);
         if (cur_kind == CH_ITEM_SEGMENT && run) {
             if (cur_attn) {
                 // the activations are the attention output: merge the splits' partials of this slice's
                 // channels here (one channel per thread) instead of in a pass of the attention's own
-                const ChainItem &it = ring[slot];
+                const ChainItem &it = CH_RING[slot];
                 const float *partial = (const float *)it.x;
                 uint16_t *xw = (uint16_t *)(aux + kChAuxX) + slot * kSliceK;
                 // a slice of 512 channels = up to four heads of 128; the weights of the splits are
@@ -288,7 +294,7 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
                 named_bar_sync<kChBarConsumers, kChConsumers>();
             }
             const bool norm = cur_norm;
-            const float inv_rms = norm ? inv_rms_s[slot] : 1.f;
+            const float inv_rms = norm ? ((const float *)(aux + kChAuxInvRms))[slot] : 1.f;
             const uint16_t *xs = (const uint16_t *)(aux + kChAuxX) + slot * kSliceK;
             const uint16_t *gs = (const uint16_t *)(aux + kChAuxGamma) + slot * kSliceK;
             // the value the tables are built from: rounded to fp16 where the separate norm kernel rounds
@@ -304,7 +310,7 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
                 constexpr int lanes_per_group = 8 >> (3 - gshift);   // g / 16 lanes: 8, 4 or 2
 #pragma unroll
                 for (int dd = 1; dd < lanes_per_group; dd <<= 1) part += __shfl_xor_sync(0xffffffffu, part, dd);
-                if ((lane & (lanes_per_group - 1)) == 0) xsum[lane / lanes_per_group] = part;
+                if ((lane & (lanes_per_group - 1)) == 0) ((float *)(aux + kChAuxXsum))[lane / lanes_per_group] = part;
             }
             {
                 const int h = warp & 1, ehi = warp >> 1;   // bank-row, top three index bits
@@ -338,7 +344,7 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
 
             float xsu[GPW];
 #pragma unroll
-            for (int uu = 0; uu < GPW; ++uu) xsu[uu] = xsum[GPW * j + (uu ^ (r >> gshift))];
+            for (int uu = 0; uu < GPW; ++uu) xsu[uu] = ((const float *)(aux + kChAuxXsum))[GPW * j + (uu ^ (r >> gshift))];
 
             // stream: ring of register tiles, loads in flight behind the one in use
             constexpr long long kStepP = kChConsumerWarps * kDuoPlaneBytes;
@@ -381,13 +387,13 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
         // arrival waits for the loads a thread has in flight
         named_bar_arrive_dyn(kChBarItemDone + slot, kChThreads);
         if (tid == 0) stamp(i, 7);
-        const bool have = mbar_wait_timed(mb_desc + 8 * (slot ^ 1), ((i + 1) >> 1) & 1, fail, budget_long);
-        if (!have || ring[slot ^ 1].kind == CH_ITEM_END) return false;
-        if (ring[slot ^ 1].kind == CH_ITEM_ATTENTION) {
+        const bool have = mbar_wait_timed(CH_MB_DESC + 8 * (slot ^ 1), ((i + 1) >> 1) & 1, CH_FAIL, CH_BUDGET_LONG);
+        if (!have || CH_RING[slot ^ 1].kind == CH_ITEM_END) return false;
+        if (CH_RING[slot ^ 1].kind == CH_ITEM_ATTENTION) {
             ++i;
             return true;
         }
-        open_item(ring[slot ^ 1]);
+        open_item(CH_RING[slot ^ 1]);
     }
 }
 
@@ -748,7 +754,7 @@ __global__ void __launch_bounds__(kChThreads, 1) decode_chain_kernel(const __gri
             if (!end_item(slot)) return;
             continue;
         }
-        if (!chain_gemv_items<Q, GPW>(a, aux, aux_u32, tbl, ring, fail, budget_long, decide, inv_rms_s, xsum, i)) return;
+        if (!chain_gemv_items<Q, GPW>(a, aux, tbl, i)) return;
     }
 }
 
