@@ -48,6 +48,7 @@
 #include <new>
 #include <vector>
 
+#include "hlq_gemv_args.cuh"
 #include "hlq_gemv_dev.cuh"
 #include "hlq_internal.h"
 
@@ -66,62 +67,6 @@ constexpr int kBarConsumers = 1;   // 512 consumer threads
 constexpr int kBarSegDone = 2;     // +slot: consumers arrive, finalizers sync (640)
 constexpr int kBarFinalizers = 6;  // 128 finalizer threads
 
-// One linear of a launch.
-struct Job {
-    const uint8_t *planes;
-    const uint16_t *meta;
-    const uint16_t *bias;
-    float *acc;           // [m][np] fp32 accumulators, zero between launches
-    unsigned *counters;   // [m][blocks]
-    const void *x;        // [m][k]
-    void *y;              // [m][n]
-    int n, k, np, slices, duos, blocks;
-    int x_dtype, y_dtype;
-    long long unit_begin; // first (slice, duo) unit of this job in the launch
-    // Optional transform of the input while the tables are built (one row of x per pass):
-    //   HLQ_INPUT_GATED_SILU:  x_eff = fp16(x2 * x / (1 + exp(-x)))
-    //   HLQ_INPUT_ADD_RMSNORM: t = x + x2 (x2 may be null), res_out = fp16(t) (may be null),
-    //                          x_eff = fp16(fp16(t) * gamma / sqrt(mean(t^2) + eps))
-    int xop;
-    float eps;
-    const void *x2;          // [m][k] fp16
-    const uint16_t *gamma;   // [k] fp16
-    uint16_t *res_out;       // [m][k] fp16, distinct from x and x2
-};
-
-struct GemvArgs {
-    const TpDev *tp;      // nullptr: no fused all-reduce
-    const Job *jobs;      // njobs descriptors in global memory, or nullptr
-    int njobs;            // 0: use `single`
-    long long total_units;
-    int *status;
-    uint32_t dyn_smem;
-    int seg_cost;         // units charged per (job, slice) when the work is split over the CTAs
-    int row_base;         // first row of x this launch serves (grid.y passes of R rows follow)
-    int y_is_f32;         // host only: fp32 outputs keep one row per pass (fp32 table entries)
-    int one_row_passes;   // host only: a job has an input transform (one row of x per pass)
-    int spin_limit;       // polls after which a bounded wait gives up
-    Job single;
-};
-
-// Descriptor of one segment, written by the control warp into shared memory.
-struct Seg {
-    const uint8_t *planes;  // first cell of the segment
-    const uint16_t *meta;   // first meta entry of the segment
-    const uint16_t *bias;
-    float *acc;             // accumulator row base of mrow
-    unsigned *counters;     // counters of mrow
-    void *y;
-    long long y_base;       // element offset of mrow in y
-    int n, np, slices, k;
-    int duo_a, duo_b;
-    int x_dtype, y_dtype;
-    int mrow, blocks;
-    int live;
-    int slice;              // slice index of the segment
-    const Job *jb;          // the job (for its input transform)
-};
-
 // aux region layout (bytes from its start)
 constexpr uint32_t kAuxX = 0;          // 2 x 512 16-bit activations
 constexpr uint32_t kAuxXsum = 2048;    // up to 16 group sums (fp32)
@@ -139,95 +84,6 @@ constexpr uint32_t kAuxXsum2 = 2816;   // two-row passes: 2 x 16 group sums
 static_assert(sizeof(TpDev) <= 256, "TpDev must fit its slot");
 static_assert(sizeof(Seg) <= kAuxSegSlot, "Seg must fit its slot");
 static_assert(kAuxGamma + 2048 <= kAuxBytes, "aux area");
-
-// ---- control warp: walks the CTA's unit range and emits segment descriptors ---------------
-// The launch's work is split over the CTAs in units of one duo, plus kSegCost units per
-// (job, slice) for what a segment costs beside its duos (the 64 KB of tables, the barriers,
-// the restart of the load ring): CTAs that get many short slices would otherwise finish last.
-// Only launches of several jobs need it (a single job's slices are all alike); there
-// GemvArgs::seg_cost = kSegCost, else 0.
-constexpr int kSegCost = 40;
-__host__ __device__ static inline long long launch_units(int slices, int duos, int seg_cost) {
-    return (long long)slices * (duos + seg_cost);
-}
-
-struct Walker {
-    const GemvArgs *a;
-    long long u, u_end;
-    int jidx;
-    Job jb;
-    int mrow;
-};
-
-__device__ __forceinline__ void walker_init(Walker &w, const GemvArgs &a, int mrow) {
-    w.a = &a;
-    w.u = a.total_units * blockIdx.x / gridDim.x;
-    w.u_end = a.total_units * (blockIdx.x + 1) / gridDim.x;
-    w.mrow = mrow;
-    w.jidx = 0;
-    if (a.njobs == 0) {
-        w.jb = a.single;
-    } else {
-        // binary search for the job that holds unit u
-        int lo = 0, hi = a.njobs - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (a.jobs[mid].unit_begin <= w.u) lo = mid; else hi = mid - 1;
-        }
-        w.jidx = lo;
-        w.jb = a.jobs[lo];
-    }
-}
-
-// Fills `sg` with the next segment and returns the activation slice to copy (or nullptr).
-template <int Q, int GPW>
-__device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &valid) {
-    sg.live = 0;
-    valid = 0;
-    if (w.u >= w.u_end) return nullptr;
-    const int seg_cost = w.a->seg_cost;
-    while (w.u >= w.jb.unit_begin + launch_units(w.jb.slices, w.jb.duos, seg_cost) && w.jidx + 1 < w.a->njobs) {
-        ++w.jidx;
-        w.jb = w.a->jobs[w.jidx];
-    }
-    const Job &jb = w.jb;
-    const long long local = w.u - jb.unit_begin;
-    const int per = jb.duos + seg_cost;
-    const int s = (int)(local / per);
-    int off = (int)(local % per);
-    if (off < seg_cost) {
-        // the range starts in the slice's set-up share: it owns the slice's first duos if it
-        // reaches them, and nothing of this slice otherwise
-        if (w.u + (seg_cost - off) >= w.u_end) {
-            w.u = w.u_end;
-            return nullptr;
-        }
-        w.u += seg_cost - off;
-        off = seg_cost;
-    }
-    const int da = off - seg_cost;
-    const long long left = w.u_end - w.u;
-    const int db = (int)((long long)(jb.duos - da) < left ? jb.duos : da + left);
-    const long long cell = (long long)s * jb.duos + da;           // in duos
-    sg.planes = jb.planes + cell * (2 * Q * kCellBytes);
-    sg.meta = jb.meta + cell * ((Q + 1) * 32 * 2 * GPW);
-    sg.bias = jb.bias;
-    sg.acc = jb.acc + (long long)w.mrow * jb.np;
-    sg.counters = jb.counters + (long long)w.mrow * jb.blocks;
-    sg.y = jb.y;
-    sg.y_base = (long long)w.mrow * jb.n;
-    sg.n = jb.n; sg.np = jb.np; sg.slices = jb.slices; sg.k = jb.k;
-    sg.duo_a = da; sg.duo_b = db;
-    sg.x_dtype = jb.x_dtype; sg.y_dtype = jb.y_dtype;
-    sg.mrow = w.mrow; sg.blocks = jb.blocks;
-    sg.live = 1;
-    sg.slice = s;
-    sg.jb = w.a->njobs == 0 ? &w.a->single : &w.a->jobs[w.jidx];
-    valid = min(kSliceK, jb.k - s * kSliceK);
-    w.u += db - da;
-    return (const uint16_t *)jb.x + (long long)w.mrow * jb.k + (long long)s * kSliceK;
-}
-
 
 // R = rows of x one pass serves: 1, or 2 with half2 table entries {row, row + 1}.
 // XOP: the instantiation that applies the jobs' input transforms (one-row passes only), kept
@@ -843,10 +699,13 @@ __global__ void __launch_bounds__(kGenThreads) lut4_gemv_kernel(const GenArgs a)
 // Host side
 // ------------------------------------------------------------------------------------------
 // scratch of the LUT GEMV alone: header, counters, accumulators for up to 16 rows of x
+// rows of accumulators a launch of m rows of x needs: the small-batch kernel keeps 8 or 16 per output row
+static int acc_rows(int m) { return m < 2 ? m : (m + 7) / 8 * 8; }
+
 static size_t lut_scratch_bytes(int m, const StreamDims &d) {
     const int mm = m < kLutMaxM ? m : kLutMaxM;
     size_t counters = ((size_t)mm * d.blocks * sizeof(unsigned) + 255) / 256 * 256;
-    size_t partial = (size_t)mm * d.np * sizeof(float);
+    size_t partial = (size_t)acc_rows(mm) * d.np * sizeof(float);
     return kWsHeader + counters + partial;
 }
 
@@ -872,15 +731,10 @@ Workspace carve_workspace(void *base, int m, const StreamDims &d) {
     return w;
 }
 
-struct DeviceInfo {
-    int sms = 0;
-    int max_dyn_smem = 0;
-    std::atomic<bool> ok{false};
-};
 static DeviceInfo g_dev[64];
-static std::mutex g_first_use;     // serializes the per-device lookups done on first use
+std::mutex g_first_use;
 
-static int device_info(int device, DeviceInfo **out) {
+int device_info(int device, DeviceInfo **out) {
     if (device < 0 || device >= 64) return HLQ_ERR_INVALID_ARGUMENT;
     DeviceInfo &d = g_dev[device];
     if (!d.ok.load(std::memory_order_acquire)) {
@@ -896,24 +750,6 @@ static int device_info(int device, DeviceInfo **out) {
         }
     }
     *out = &d;
-    return HLQ_OK;
-}
-
-template <typename KernelT, typename ArgsT>
-static int launch_pdl(KernelT kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                      const ArgsT &args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    HLQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, args));
-    count_launch();
     return HLQ_OK;
 }
 
@@ -954,11 +790,18 @@ static int launch_lut8_rows(int q, int gpw, const GemvArgs &a, dim3 grid, cudaSt
 // entries of such a pass are rounded to fp16 (2^-11, as the reference's tables are), which is
 // below the rounding of a 16-bit output; fp32 outputs therefore keep one row per pass and
 // fp32 entries, and so does the fused all-reduce.
-static int launch_lut8_any(int q, int gpw, const GemvArgs &a_in, dim3 grid, cudaStream_t stream) {
+//
+// Plain launches of 2 <= m <= 16 rows at q = 2 or 3 with 16-bit outputs go to the small-batch kernel
+// instead (hlq_batch.cu: one pass over the weights for all rows; its weights are rounded to fp16,
+// which is below the rounding of a 16-bit output but not of an fp32 one), unless `lut_only` (a
+// weight whose extra bit-plane has already been added into accumulators of the LUT kernel's layout).
+static int launch_lut8_any(int q, int gpw, const GemvArgs &a_in, dim3 grid, cudaStream_t stream,
+                           bool lut_only = false) {
     const int m = (int)grid.y;
     GemvArgs a = a_in;
     a.row_base = 0;
     if (a.one_row_passes) return launch_lut8_rows<1, true>(q, gpw, a, grid, stream);
+    if (!lut_only && !a.tp && !a.y_is_f32 && batch_mma_supported(q, m)) return launch_batch_mma(q, gpw, a, (int)grid.x, m, stream);
     if (m < 2 || a.tp || a.y_is_f32) return launch_lut8_rows<1, false>(q, gpw, a, grid, stream);
     int rc = launch_lut8_rows<2, false>(q, gpw, a, dim3(grid.x, m / 2), stream);
     if (rc || !(m & 1)) return rc;
@@ -978,6 +821,7 @@ static void fill_job(Job &j, const hlq_weight *w, const StreamDims &d, const voi
     j.n = w->n; j.k = w->k; j.np = d.np; j.slices = d.slices; j.duos = d.duos; j.blocks = d.blocks;
     j.x_dtype = x_dtype; j.y_dtype = y_dtype;
     j.unit_begin = unit_begin;
+    j.unit_begin_chunked = unit_begin;      // a single job starts at 0 either way; groups set their own
     j.xop = HLQ_INPUT_PLAIN;
     j.eps = 0.f;
     j.x2 = nullptr;
@@ -1029,6 +873,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         a.jobs = nullptr;
         a.njobs = 0;
         a.total_units = launch_units(d.slices, d.duos, 0);
+        a.total_units_chunked = launch_units_chunked(d.slices, d.duos, kChunkDuos, kChunkSegCost);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
         a.spin_limit = kDefaultSpinLimit;
@@ -1043,7 +888,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         // a weight with the extra bit-plane: its blocks' sums go into the accumulators first
         rc = launch_sparse_plane(w, mc, a.single.x, x_dtype, ws.partial, d.np, nullptr, y_dtype, stream);
         if (rc) return rc;
-        rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream);
+        rc = launch_lut8_any(w->q, d.gpw, a, dim3(ctas, mc), stream, w->sp_pairs != 0);
         if (rc) return rc;
     }
     return HLQ_OK;
@@ -1107,6 +952,7 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         a.jobs = nullptr;
         a.njobs = 0;
         a.total_units = launch_units(d.slices, d.duos, 0);
+        a.total_units_chunked = launch_units_chunked(d.slices, d.duos, kChunkDuos, kChunkSegCost);
         a.status = ws.status;
         a.dyn_smem = kLut8DynSmem;
         a.spin_limit = kDefaultSpinLimit;
@@ -1333,6 +1179,7 @@ struct hlq_group {
     int count = 0, max_m = 1;
     int q = 0, gpw = 0;
     long long total_units = 0;    // with the per-slice set-up share (launch_units)
+    long long total_units_chunked = 0;   // under the small-batch kernel's walk (launch_units_chunked)
     long long duo_units = 0;      // (slice, duo) pairs
     int seg_cost = 0;
     bool one_row_passes = false;  // a member has an input transform
@@ -1378,7 +1225,7 @@ int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weight
         coff[i] = off;
         off += ((size_t)max_m * d.blocks * sizeof(unsigned) + 255) / 256 * 256;
         poff[i] = off;
-        off += ((size_t)max_m * d.np * sizeof(float) + 255) / 256 * 256;
+        off += ((size_t)acc_rows(max_m) * d.np * sizeof(float) + 255) / 256 * 256;
         units += (long long)d.slices * d.duos;
     }
     g->scratch_bytes = off;
@@ -1392,16 +1239,19 @@ int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weight
     if (!rc) rc = note_cuda(cudaMemset(g->d_scratch, 0, off));
     if (!rc) {
         g->seg_cost = count > 1 ? kSegCost : 0;
-        long long ub = 0;
+        long long ub = 0, ubc = 0;
         for (int i = 0; i < count; ++i) {
             const hlq_weight *w = weights[i];
             const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
             fill_job(g->jobs_host[i], w, d, nullptr, HLQ_F16, nullptr, HLQ_F16,
                      (float *)(g->d_scratch + poff[i]), (unsigned *)(g->d_scratch + coff[i]), ub);
+            g->jobs_host[i].unit_begin_chunked = ubc;
             ub += launch_units(d.slices, d.duos, g->seg_cost);
+            ubc += launch_units_chunked(d.slices, d.duos, kChunkDuos, kChunkSegCost);
             g->duo_units += (long long)d.slices * d.duos;
         }
         g->total_units = ub;
+        g->total_units_chunked = ubc;
     }
     if (prev >= 0) cudaSetDevice(prev);
     if (rc) {
@@ -1460,6 +1310,7 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.jobs = g->d_jobs;
     a.njobs = g->count;
     a.total_units = g->total_units;
+    a.total_units_chunked = g->total_units_chunked;
     a.seg_cost = g->seg_cost;
     a.status = (int *)g->d_scratch;
     a.dyn_smem = kLut8DynSmem;
