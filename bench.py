@@ -468,7 +468,8 @@ def batches_object(dev, args, stream, steps, warmup):
                         "launches_per_step": r["launches_per_step"]}
     out = {"workload": f"llama3-8b projection set w3g128, {args.layers} layers, rows of activations 1/4/8/16",
            "algorithmic_bytes_per_step": ps.total_bytes, "rows": rows,
-           "note": "bytes do not grow with the rows; two rows share every table lookup (passes of two rows)"}
+           "note": "bytes do not grow with the rows; 1 row: LUT kernel; 4, 8, 16 rows: one pass over the weights, "
+                   "register dequantization + mma.sync (batch_mma_kernel), bound by the integer pipe"}
     del ps
     return out
 

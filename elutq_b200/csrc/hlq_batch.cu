@@ -1,4 +1,4 @@
-// Small batches (2..16 rows of activations) over HLQ weights in the streaming layout, sm_100a:
+// Small batches (3..16 rows of activations) over HLQ weights in the streaming layout, sm_100a:
 // the weights are streamed ONCE per call, whatever the number of rows.
 //
 // Replaces, for small m, the reference's batched path
@@ -28,9 +28,15 @@
 //     [output row][row of x] with 128-bit reductions; completion counters per block of 32 rows
 //     and the finalizing pass are those of the LUT kernel, run by one warp.
 //
-// The tensor work is tiny (2 * m * n * k): the kernel is bound by the dequantization's integer
-// instructions and by HBM, not by the tensor pipe, which is why the register-fed mma.sync is
-// used here instead of tcgen05 (whose operands would have to go through shared memory or TMEM).
+// What bounds it: the integer pipe.  A sub-partition issues one prmt / lop3 / shf every two cycles,
+// and a duo costs each lane about 540 of them (256 table permutes, 160 for the selectors, the
+// rest for the layout's permutation, the tables and addressing).  The register-fed
+// mma.sync.m16n8k16 takes 8 more cycles of the same sub-partition per instruction on this part
+// and does not overlap with the integer work (measured: 8.0 cycles back to back; 12 / 19 / 36
+// with 4 / 8 / 16 permutes between two of them), i.e. another 256 or 512 cycles per duo for up
+// to 8 or 16 rows of x.  Measured duo rates match that sum (342 and 438 cycles per duo and SM).
+// tcgen05 would take the matrix work off the sub-partitions but wants its weight operand in
+// shared memory or TMEM, i.e. one more store per dequantized register.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -167,7 +173,8 @@ __device__ __forceinline__ void build_tables(const Tile<Q, GPW> &t, int ou, int 
 // `bs`: this lane's base into the fragment-ordered activations (its row of x and quarter).
 template <int Q, int GPW, int NT>
 __device__ __forceinline__ void mma_tile(const Tile<Q, GPW> &t, uint32_t bs, int r, uint32_t usel,
-                                         float (&acc)[NT][4]) {
+                                         float (&acc)[4 / NT][NT][4]) {
+    constexpr int kChains = 4 / NT;     // independent accumulators per block of 8 rows of x
     uint32_t pw[2][Q][4];
 #pragma unroll
     for (int ou = 0; ou < 2; ++ou)
@@ -221,7 +228,9 @@ __device__ __forceinline__ void mma_tile(const Tile<Q, GPW> &t, uint32_t bs, int
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     const uint2 b = lds_v2(bs + (uint32_t)((c * 8 + s * 2 + h) * 8) + nt * 8 * kBmRowStride);
-                    mma_16816(acc[nt], a[0][0], a[1][0], a[0][1], a[1][1], b.x, b.y);
+                    // consecutive instructions add into different accumulators: one whose input is
+                    // the result of the one before would wait out the tensor pipe's latency
+                    mma_16816(acc[(2 * s + h) % kChains][nt], a[0][0], a[1][0], a[0][1], a[1][1], b.x, b.y);
                 }
             }
         }
@@ -454,8 +463,17 @@ __global__ void __launch_bounds__(kBmThreads, 1) batch_mma_kernel(const __grid_c
         open_segment(ring[0]);
     }
     auto run_tile = [&](const Tile<Q, GPW> &t, int d, uint32_t bs) {
-        float acc[NT][4] = {};
-        mma_tile<Q, GPW, NT>(t, bs, r, usel, acc);
+        float accs[4 / NT][NT][4] = {};
+        mma_tile<Q, GPW, NT>(t, bs, r, usel, accs);
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[nt][e] = accs[0][nt][e];
+#pragma unroll
+                for (int ch = 1; ch < 4 / NT; ++ch) acc[nt][e] += accs[ch][nt][e];
+            }
         // lanes j, j ^ 1 hold rows of x (2j, 2j + 1) of output rows r and r + 8: after the exchange
         // the even lane owns four rows of x of output row r, the odd lane those of row r + 8
         float *dst = accb + (long long)d * (16 * MT);
@@ -512,7 +530,9 @@ int launch_inst(const GemvArgs &args, int ctas, cudaStream_t stream) {
 
 }  // namespace
 
-bool batch_mma_supported(int q, int m) { return (q == 2 || q == 3) && m >= 2 && m <= kLutMaxM; }
+// Two rows of x are cheaper as one pass of the LUT kernel with half2 table entries (0.65 of this
+// kernel's time on the Llama-3-8B projection set); from three rows on this kernel wins.
+bool batch_mma_supported(int q, int m) { return (q == 2 || q == 3) && m >= 3 && m <= kLutMaxM; }
 
 // All `m` rows of x of the launch in one pass.  The accumulators of a job are [np][8 or 16] fp32
 // (rows of x innermost), the counters those of its first row.

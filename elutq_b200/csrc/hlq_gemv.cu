@@ -791,7 +791,7 @@ static int launch_lut8_rows(int q, int gpw, const GemvArgs &a, dim3 grid, cudaSt
 // below the rounding of a 16-bit output; fp32 outputs therefore keep one row per pass and
 // fp32 entries, and so does the fused all-reduce.
 //
-// Plain launches of 2 <= m <= 16 rows at q = 2 or 3 with 16-bit outputs go to the small-batch kernel
+// Plain launches of 3 <= m <= 16 rows at q = 2 or 3 with 16-bit outputs go to the small-batch kernel
 // instead (hlq_batch.cu: one pass over the weights for all rows; its weights are rounded to fp16,
 // which is below the rounding of a 16-bit output but not of an fp32 one), unless `lut_only` (a
 // weight whose extra bit-plane has already been added into accumulators of the LUT kernel's layout).

@@ -209,8 +209,12 @@ int hlq_workspace_status(const void *d_workspace, void *stream, int *kernel_stat
  * {F16, BF16, F32}; accumulation is fp32.  k and n must equal the handle's shard sizes.
  * With HLQ_SHARD_COLS the result is this rank's partial sum.  Not re-entrant on one
  * workspace.  x and y must be 16-byte aligned.
+ * Kernels by m (streaming layout): 1 or 2 rows, and fp32 outputs up to 16 rows: table-lookup
+ * GEMV; 3..16 rows with 16-bit outputs at 2 or 3 bits: one pass over the weights for all rows
+ * (dequantization in registers + mma.sync; the weights are rounded to fp16 there); more rows:
+ * dequantization + tcgen05 GEMM.
  * Replaces: arm_gemm, C++/ops/include/arm/arm_gemm.h:4-14 (dispatch at
- * C++/ops/src/arm/arm_gemm.cpp:871-924). */
+ * C++/ops/src/arm/arm_gemm.cpp:871-924; GEMV worker :248-308, GEMM worker :362-387). */
 int hlq_linear_forward(int m, int k, int n, const void *d_x, int x_dtype, void *d_y, int y_dtype,
                        void *d_workspace, size_t workspace_bytes, const hlq_weight *w,
                        void *stream);
@@ -229,10 +233,11 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
  * cudaMalloc/cudaFree.  The scratch (status word, completion counters, fp32 accumulators)
  * lives in a fixed HLQ_STATIC_SCRATCH_BYTES array inside the library, which every GPU that
  * loads the library holds until the process exits.  The call allocates nothing.
- *  - Limit: the scratch of one launch, 256 + 128 * r * ceil(n/32) + 4 * r * 32 * ceil(n/32)
- *    bytes with r = min(m, 16) rows per launch (counters rounded up to 256 bytes; more rows run
- *    as several launches of 16), must fit HLQ_STATIC_SCRATCH_BYTES, else HLQ_ERR_WORKSPACE
- *    (m = 1: n up to ~250 000 rows; m >= 16: n up to ~15 000).  Weights in the exported
+ *  - Limit: the scratch of one launch, 256 + 4 * r * ceil(n/32) (rounded up to 256) +
+ *    4 * r8 * 32 * ceil(n/32) bytes with r = min(m, 16) rows per launch and r8 = r rounded up to
+ *    8 when r >= 2 (more rows run as several launches of 16), must fit
+ *    HLQ_STATIC_SCRATCH_BYTES, else HLQ_ERR_WORKSPACE (m = 1: n up to ~250 000 rows;
+ *    m >= 9: n up to ~15 000).  Weights in the exported
  *    layout: HLQ_ERR_UNSUPPORTED.
  *  - The first call on a device looks the array's address up (with the weight's device
  *    current, as for hlq_linear_forward); make that first call before any stream capture.

@@ -1,4 +1,4 @@
-"""The small-batch kernel (2..16 rows of activations, one pass over the weights) against the oracle.
+"""The small-batch kernel (3..16 rows of activations, one pass over the weights) against the oracle.
 
 Tolerance: 1e-3 normwise for 16-bit outputs, as for the other kernels (the kernel rounds the
 dequantized weights to fp16 and accumulates in fp32).
@@ -41,7 +41,7 @@ def forward(mod, x, out_dtype=torch.float16):
 @pytest.mark.parametrize("q", [2, 3])
 @pytest.mark.parametrize("g", [128, 64, 32])
 def test_every_row_count(L, q, g):
-    """2..16 rows of x, every group size of the streaming layout, ragged n and k, bias, signed scales."""
+    """2..16 rows of x (two rows: the LUT kernel's paired pass), every group size of the streaming layout, ragged n and k, bias, signed scales."""
     d = O.synth_linear(200, 1152, q, g, m=16, seed=3 * q + g, bias=True, signed_alpha=True)
     mod = make(d, g, max_batch=16)
     ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
