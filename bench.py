@@ -562,7 +562,8 @@ def run_gemv(args):
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": per_gpu / peaks["hbm"], "traffic": traffic,
                      "traffic_source": "ncu capture of a 2-layer launch, scaled by algorithmic bytes",
-                     "peak_source": f"of {peaks['kind']}", "kernel": "lut8_gemv_kernel",
+                     "peak_source": f"of {peaks['kind']}",
+                     "kernel": "batch_mma_kernel" if (args.batch >= 3 and args.bits in (2, 3)) else "lut8_gemv_kernel",
                      "launches_per_step": int(top["launches_per_step"]),
                      "avg_launch_us": sec * 1e6 / max(1, top["launches_per_step"])},
         "error_measure": NORMWISE,
