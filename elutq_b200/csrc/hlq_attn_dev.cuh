@@ -330,28 +330,62 @@ __device__ __forceinline__ bool attention_unit(const AttnArgs &a, int hk, int sp
     return true;
 }
 
-// The same unit for a caller that merges the splits itself (the decode chain: the linear that
-// consumes the attention output merges them while it loads its activations).  Differences from
-// attention_unit: the token's position `pos` (already clamped to the cache) and the rotary table
-// `rope` come from the caller; the loads of the first K/V tile are issued BEFORE `wait_inputs()`
-// returns (the cache does not depend on this token's q, k, v; the row of the new position is
-// taken from the new k and v instead of from the prefetched tile); the unit ends when its
-// partial (unnormalized output, running max and sum per head) is written to a.partial: no
-// counter, no merge, a.out is not written.  `wait_inputs()` is called by all threads, returns
-// the same value in all of them once q, k, v may be read, false to abandon the unit.
-template <int D, int S, typename Sync, typename Wait>
-__device__ __forceinline__ void attention_partial_unit(const AttnArgs &a, int hk, int split, int nsplit,
-                                                       AttnSmem<D> &sm, int tid, Sync sync, const float2 *rope,
-                                                       int pos, Wait wait_inputs, unsigned long long *stamps = nullptr) {
-    constexpr int T = D * S;
-    constexpr int KV = D / 8 / S;
-    static_assert(S == 1 || S == 2 || S == 4, "threads per position");
-    static_assert(KV >= 1 && (S - 1) * kMaxGroup * D * 4 <= D * D * 2, "the partial sums reuse the V tile");
-    auto &qs = sm.qs;
-    auto &pw = sm.pw;
-    __half *vs = sm.vs;
-    float *alpha = sm.alpha, *m_run = sm.m_run, *l_run = sm.l_run;
-    const int lane = tid & 31, warp = tid >> 5;
+// The unit for a caller that merges the splits itself (the decode chain: the linear that consumes
+// the attention output merges them while it loads its activations), heads of 128 channels, 512
+// threads, on the tensor cores.  Differences from attention_unit:
+//   * the token's position `pos` (already clamped to the cache) and the rotary table `rope` come
+//     from the caller; the loads of the first K/V tile are issued BEFORE `wait_inputs()` returns
+//     (the cache does not depend on this token's q, k, v; the row of the new position is taken
+//     from the new k and v instead of from the prefetched tile);
+//   * scores: K rows go from global memory straight into A fragments of mma.sync.m16n8k16 (warp w
+//     < 8 owns positions 16w .. 16w+15 of the tile; a lane's 16-byte loads are channels
+//     8 (tig + 4j) .. +7 of rows gid and gid + 8 - the instruction's k index is only a label, the
+//     roped queries in shared memory are read in the same order), B = the group's query heads
+//     (n = 8 = kMaxGroup), D = [position][head] fp32, scaled afterwards;
+//   * weighted sum: the V tile comes into shared memory by cp.async, its transposed 16 x 16 blocks
+//     are A fragments (ldmatrix.trans), B = the fp16 weights [position][head], D = [channel][head];
+//     warps w and w + 8 share the positions of a tile for channels 16 (w & 7) .. +15;
+//   * the unit ends when its partial (unnormalized output, running max and sum per head) is
+//     written to a.partial: no counter, no merge, a.out is not written.
+// `sync` is a barrier over the 512 threads; `wait_inputs()` is called by all threads, returns the
+// same value in all of them once q, k, v may be read, false to abandon the unit.
+struct AttnMmaSmem {
+    static constexpr int kPad = 136;                 // halves per padded row of 128: 272 bytes
+    __align__(16) __half q16[kMaxGroup][kPad];       // roped queries (rows >= group: zero)
+    __align__(16) float pw[128][kMaxGroup];          // scores of a tile
+    __align__(16) __half pt[kMaxGroup][kPad];        // weights of a tile, [head][position]
+    __align__(16) __half vs[128 * kPad];             // the V tile: [position][channel], rows 272 bytes apart
+    __align__(16) float red[8][32][4];               // accumulators of warps 8..15
+    float alpha[kMaxGroup], m_run[kMaxGroup], l_run[kMaxGroup];
+    __align__(16) __half knew[128], vnew[128];       // the new token's roped k row and v row
+};
+
+__device__ __forceinline__ void attn_cp_async_16(void *dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void attn_cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void attn_mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void attn_ldmatrix_x4_trans(uint32_t (&r)[4], const void *row_smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(row_smem)));
+}
+
+template <typename Sync, typename Wait>
+__device__ __forceinline__ void attention_partial_unit(const AttnArgs &a, int hk, int split, int nsplit, AttnMmaSmem &sm,
+                                                       int tid, Sync sync, const float2 *rope, int pos,
+                                                       Wait wait_inputs, unsigned long long *stamps = nullptr) {
+    constexpr int D = 128, P = AttnMmaSmem::kPad;
+    const int lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
     auto mark = [&](int k) {
         if (stamps && tid == 0) {
             unsigned long long t;
@@ -365,27 +399,39 @@ __device__ __forceinline__ void attention_partial_unit(const AttnArgs &a, int hk
     const int t0 = split * per, t1 = min(nkv, t0 + per);
     const size_t row_stride = (size_t)a.pos_stride;
     const size_t head_off = (size_t)hk * (size_t)a.head_stride;
-    const int sp = tid / S, part = tid % S;      // score phase: position of the tile, part of its row
-    const int ch = tid % D, pg = tid / D;        // V phase: channel, group of positions
 
-    // the first tile's loads, before the inputs are there
-    uint4 kreg[KV], vreg[KV];
-    auto load_tile_regs = [&](int tile, int ntile) {
-        if (sp < ntile) {
-            const uint4 *kr = (const uint4 *)(a.kcache + (size_t)(tile + sp) * row_stride + head_off) + part;
+    uint4 kf[2][4];      // warps 0..7: rows gid, gid + 8 of the warp's 16 positions, channels 8 (tig + 4j) .. +7
+    auto load_tile = [&](int tile, int ntile) {
+        if (warp < 8) {
 #pragma unroll
-            for (int c = 0; c < KV; ++c) kreg[c] = kr[c * S];
+            for (int rr = 0; rr < 2; ++rr) {
+                const int p = 16 * warp + gid + 8 * rr;
+                if (p < ntile) {
+                    const uint4 *kr = (const uint4 *)(a.kcache + (size_t)(tile + p) * row_stride + head_off);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) kf[rr][j] = kr[tig + 4 * j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) kf[rr][j] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
         }
+        // 128 rows x 16 chunks of 16 bytes, four per thread; rows past the tile are zero (a weight of
+        // zero must not meet a NaN)
 #pragma unroll
-        for (int u = 0; u < KV; ++u) {
-            const int idx = tid + u * T, t = idx / (D / 8), c8 = idx % (D / 8);
-            vreg[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (t < ntile)
-                vreg[u] = *(const uint4 *)(a.vcache + (size_t)(tile + t) * row_stride + head_off + 8 * c8);
+        for (int u = 0; u < 4; ++u) {
+            const int idx = tid + 512 * u, t = idx >> 4, c = idx & 15;
+            __half *dst = sm.vs + t * P + 8 * c;
+            if (t < ntile) attn_cp_async_16(dst, a.vcache + (size_t)(tile + t) * row_stride + head_off + 8 * c);
+            else *(uint4 *)dst = make_uint4(0u, 0u, 0u, 0u);
         }
     };
-    if (t0 < t1) load_tile_regs(t0, min(D, t1 - t0));
-    if (!wait_inputs()) return;
+    sync();            // the shared memory may still be in use by whatever ran before the unit
+    if (t0 < t1) load_tile(t0, min(D, t1 - t0));
+    if (!wait_inputs()) {
+        attn_cp_async_wait_all();
+        return;
+    }
     mark(0);
 
     // RoPE: pair (j, j + D/2); q, k and v of this token are loaded together
@@ -402,10 +448,8 @@ __device__ __forceinline__ void attention_partial_unit(const AttnArgs &a, int hk
         const float k1 = __half2float(__ldcg(kp + tid)), k2 = __half2float(__ldcg(kp + tid + D / 2));
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g) {
-            if (g < G) {
-                qs[g][tid] = __half2float(__float2half_rn(q1[g] * cs - q2[g] * sn)) * a.scale;
-                qs[g][tid + D / 2] = __half2float(__float2half_rn(q1[g] * sn + q2[g] * cs)) * a.scale;
-            }
+            sm.q16[g][tid] = g < G ? __float2half_rn(q1[g] * cs - q2[g] * sn) : __float2half_rn(0.f);
+            sm.q16[g][tid + D / 2] = g < G ? __float2half_rn(q1[g] * sn + q2[g] * cs) : __float2half_rn(0.f);
         }
         const __half ka = __float2half_rn(k1 * cs - k2 * sn), kb = __float2half_rn(k1 * sn + k2 * cs);
         sm.knew[tid] = ka;
@@ -426,121 +470,125 @@ __device__ __forceinline__ void attention_partial_unit(const AttnArgs &a, int hk
             vc[j] = va;
             vc[j + D / 2] = vb;
         }
+    } else if (tid < D + kMaxGroup) {
+        const int g = tid - D;
+        sm.m_run[g] = -INFINITY;
+        sm.l_run[g] = 0.f;
+        sm.alpha[g] = 0.f;
+    } else if (tid >= 256) {
+        // weights of heads the group does not have stay zero
+        for (int i = tid - 256; i < kMaxGroup * P; i += 256) (&sm.pt[0][0])[i] = __float2half_rn(0.f);
     }
-    if (tid < kMaxGroup) {
-        m_run[tid] = -INFINITY;
-        l_run[tid] = 0.f;
-        alpha[tid] = 0.f;
-    }
-    float acc[kMaxGroup];
-#pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g) acc[g] = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};       // channels 16 (warp & 7) + gid (+ 8), heads 2 tig, 2 tig + 1
+    attn_cp_async_wait_all();
     sync();
     mark(1);
 
     for (int tile = t0; tile < t1; tile += D) {
         const int ntile = min(D, t1 - tile);
-        if (tile != t0) load_tile_regs(tile, ntile);
+        if (tile != t0) {
+            load_tile(tile, ntile);
+            attn_cp_async_wait_all();
+        }
         // the new position's row: from the new k / v, not from the (possibly prefetched) cache
-        if (tile + sp == pos) {
+        if (warp < 8) {
 #pragma unroll
-            for (int c = 0; c < KV; ++c) kreg[c] = *(const uint4 *)(sm.knew + 8 * (c * S + part));
+            for (int rr = 0; rr < 2; ++rr)
+                if (tile + 16 * warp + gid + 8 * rr == pos) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) kf[rr][j] = *(const uint4 *)(sm.knew + 8 * (tig + 4 * j));
+                }
         }
+        if (pos >= tile && pos < tile + ntile && tid >= 256 && tid < 256 + 16)
+            *(uint4 *)(sm.vs + (pos - tile) * P + 8 * (tid - 256)) = *(const uint4 *)(sm.vnew + 8 * (tid - 256));
+        // scores of the warp's 16 positions for all heads of the group
+        if (warp < 8) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int u = 0; u < KV; ++u) {
-            const int idx = tid + u * T, t = idx / (D / 8), c8 = idx % (D / 8);
-            if (tile + t == pos) vreg[u] = *(const uint4 *)(sm.vnew + 8 * c8);
-        }
-        // scores, one query head at a time (one accumulator live instead of eight): S threads
-        // per position, then a shuffle reduction among them
-#pragma unroll 1
-        for (int g = 0; g < G; ++g) {
-            float s = 0.f;
-            if (sp < ntile) {
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t k0[4] = {kf[0][j].x, kf[0][j].y, kf[0][j].z, kf[0][j].w};
+                const uint32_t k1[4] = {kf[1][j].x, kf[1][j].y, kf[1][j].z, kf[1][j].w};
 #pragma unroll
-                for (int c = 0; c < KV; ++c) {
-                    const __half2 *kh = (const __half2 *)&kreg[c];
-                    const int c0 = 8 * (c * S + part);
-                    const float4 qa = *(const float4 *)&qs[g][c0], qb = *(const float4 *)&qs[g][c0 + 4];
-                    const float2 f0 = __half22float2(kh[0]), f1 = __half22float2(kh[1]);
-                    const float2 f2 = __half22float2(kh[2]), f3 = __half22float2(kh[3]);
-                    s += f0.x * qa.x + f0.y * qa.y + f1.x * qa.z + f1.y * qa.w + f2.x * qb.x + f2.y * qb.y +
-                         f3.x * qb.z + f3.y * qb.w;
+                for (int e = 0; e < 2; ++e) {
+                    const uint2 b = *(const uint2 *)(&sm.q16[gid][8 * (tig + 4 * j) + 4 * e]);
+                    attn_mma_16816(c, k0[2 * e], k1[2 * e], k0[2 * e + 1], k1[2 * e + 1], b.x, b.y);
                 }
             }
-#pragma unroll
-            for (int dd = 1; dd < S; dd <<= 1) s += __shfl_xor_sync(0xffffffffu, s, dd);
-            if (sp >= ntile) s = -INFINITY;
-            if (part == 0) pw[sp][g] = s;
+            const int p0 = 16 * warp + gid;
+            const float sc = a.scale;
+            *(float2 *)&sm.pw[p0][2 * tig] = p0 < ntile ? make_float2(c[0] * sc, c[1] * sc) : make_float2(-INFINITY, -INFINITY);
+            *(float2 *)&sm.pw[p0 + 8][2 * tig] =
+                p0 + 8 < ntile ? make_float2(c[2] * sc, c[3] * sc) : make_float2(-INFINITY, -INFINITY);
         }
-#pragma unroll
-        for (int u = 0; u < KV; ++u) ((uint4 *)vs)[tid + u * T] = vreg[u];
         sync();
         mark(2);
-        for (int g = warp; g < G; g += T / 32) {
+        // running max and sum per head; scores become fp16 weights [head][position]
+        for (int g = warp; g < G; g += 16) {
             float sv[D / 32], tmax = -INFINITY;
 #pragma unroll
             for (int i = 0; i < D / 32; ++i) {
-                sv[i] = pw[lane + 32 * i][g];
+                sv[i] = sm.pw[lane + 32 * i][g];
                 tmax = fmaxf(tmax, sv[i]);
             }
             tmax = warp_max(tmax);
-            const float mold = m_run[g], mnew = fmaxf(mold, tmax);
+            const float mold = sm.m_run[g], mnew = fmaxf(mold, tmax);
             float psum = 0.f;
 #pragma unroll
             for (int i = 0; i < D / 32; ++i) {
                 const float p = expf(sv[i] - mnew);       // exp(-inf) = 0 for the positions past the tile
-                pw[lane + 32 * i][g] = p;
-                psum += p;
+                const __half ph = __float2half_rn(p);
+                sm.pt[g][lane + 32 * i] = ph;
+                psum += __half2float(ph);                 // the sum of what the weighted sum will use
             }
             psum = warp_sum(psum);
             if (lane == 0) {
                 const float al = expf(mold - mnew);        // 0 on the first tile (mold = -inf)
-                alpha[g] = al;
-                m_run[g] = mnew;
-                l_run[g] = l_run[g] * al + psum;
+                sm.alpha[g] = al;
+                sm.m_run[g] = mnew;
+                sm.l_run[g] = sm.l_run[g] * al + psum;
             }
         }
         sync();
         {
+            const int dw = warp & 7, kh = warp >> 3;
+            const float a0 = sm.alpha[2 * tig], a1 = sm.alpha[2 * tig + 1];
+            acc[0] *= a0; acc[1] *= a1; acc[2] *= a0; acc[3] *= a1;
+            const int mi = lane >> 3;
 #pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) acc[g] *= alpha[g];
-            const int tb = pg * (D / S), te = min(ntile, tb + D / S);
-#pragma unroll 8
-            for (int t = tb; t < te; ++t) {
-                const float v = __half2float(vs[t * D + ch]);
-                const float4 pa = *(const float4 *)&pw[t][0], pb = *(const float4 *)&pw[t][4];
-                acc[0] += pa.x * v; acc[1] += pa.y * v; acc[2] += pa.z * v; acc[3] += pa.w * v;
-                acc[4] += pb.x * v; acc[5] += pb.y * v; acc[6] += pb.z * v; acc[7] += pb.w * v;
+            for (int ks = 0; ks < 4; ++ks) {
+                const int base = 16 * (4 * kh + ks);
+                if (base < ntile) {                 // uniform in the warp
+                    uint32_t vf[4];
+                    attn_ldmatrix_x4_trans(vf, sm.vs + (base + (lane & 7) + 8 * (mi >> 1)) * P + 16 * dw + 8 * (mi & 1));
+                    const uint32_t b0 = *(const uint32_t *)&sm.pt[gid][base + 2 * tig];
+                    const uint32_t b1 = *(const uint32_t *)&sm.pt[gid][base + 2 * tig + 8];
+                    attn_mma_16816(acc, vf[0], vf[1], vf[2], vf[3], b0, b1);
+                }
             }
         }
         sync();
     }
     mark(3);
-    if (S > 1) {
-        float *part_acc = (float *)vs;           // [S - 1][kMaxGroup][D]
-        if (pg > 0) {
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g) part_acc[((pg - 1) * kMaxGroup + g) * D + ch] = acc[g];
-        }
-        sync();
-        if (pg == 0) {
-#pragma unroll
-            for (int g = 0; g < kMaxGroup; ++g)
-#pragma unroll
-                for (int o = 0; o < S - 1; ++o) acc[g] += part_acc[(o * kMaxGroup + g) * D + ch];
-        }
-    }
+    // warps w + 8 hand their half of the positions to warps w
+    if (warp >= 8) *(float4 *)&sm.red[warp - 8][lane][0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    sync();
     // this split's partial: a share without positions (t0 >= t1) publishes max = -inf, sum = 0
     float *mine = a.partial + ((size_t)hk * nsplit + split) * G * (D + 2);
-    if (tid < D) {
-        for (int g = 0; g < G; ++g) {
-            mine[(size_t)g * (D + 2) + tid] = acc[g];
-            if (tid == 0) {
-                mine[(size_t)g * (D + 2) + D] = m_run[g];
-                mine[(size_t)g * (D + 2) + D + 1] = l_run[g];
-            }
+    if (warp < 8) {
+        const float4 o = *(const float4 *)&sm.red[warp][lane][0];
+        const int d0 = 16 * warp + gid;
+        if (2 * tig < G) {
+            mine[(size_t)(2 * tig) * (D + 2) + d0] = acc[0] + o.x;
+            mine[(size_t)(2 * tig) * (D + 2) + d0 + 8] = acc[2] + o.z;
         }
+        if (2 * tig + 1 < G) {
+            mine[(size_t)(2 * tig + 1) * (D + 2) + d0] = acc[1] + o.y;
+            mine[(size_t)(2 * tig + 1) * (D + 2) + d0 + 8] = acc[3] + o.w;
+        }
+    } else if (tid - 256 < G) {
+        const int g = tid - 256;
+        mine[(size_t)g * (D + 2) + D] = sm.m_run[g];
+        mine[(size_t)g * (D + 2) + D + 1] = sm.l_run[g];
     }
     mark(4);
 }

@@ -151,7 +151,7 @@ constexpr uint32_t kChAuxRope = 4096;     // 64 x {cos, sin} of the token's posi
 constexpr uint32_t kChAuxMerge = 4608;    // 4 x 64 floats: normalized weights of the attention splits of a slice's heads
 constexpr uint32_t kChAuxGamma = 6144;    // 2 slots x 512 fp16 norm weights
 static_assert(sizeof(ChainItem) == kChAuxItemSlot, "a ChainItem is one ring slot (and one bulk copy)");
-static_assert(sizeof(AttnSmem<128>) <= kChTableBytes, "the attention unit borrows the table block");
+static_assert(sizeof(AttnMmaSmem) <= kChTableBytes, "the attention unit borrows the table block");
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned *p) {
     unsigned v;
@@ -205,7 +205,7 @@ struct ChainWait {
 __device__ __noinline__ bool chain_attention(const AttnArgs *args, int hk, int split, int nsplit, unsigned char *smem,
                                              int tid, const float2 *rope, int pos, ChainWait w,
                                              unsigned long long *stamps) {
-    AttnSmem<128> &sm = *(AttnSmem<128> *)smem;
+    AttnMmaSmem &sm = *(AttnMmaSmem *)smem;
     auto sync = [] { named_bar_sync<kChBarConsumers, kChConsumers>(); };
     auto wait_inputs = [&]() {
         const bool got = mbar_wait_timed(w.mbar, w.parity, w.fail, w.budget);
@@ -213,7 +213,7 @@ __device__ __noinline__ bool chain_attention(const AttnArgs *args, int hk, int s
         named_bar_sync<kChBarConsumers, kChConsumers>();
         return *w.decide != 0;
     };
-    attention_partial_unit<128, 4>(*args, hk, split, nsplit, sm, tid, sync, rope, pos, wait_inputs, stamps);
+    attention_partial_unit(*args, hk, split, nsplit, sm, tid, sync, rope, pos, wait_inputs, stamps);
     return *w.decide != 0;
 }
 

@@ -44,11 +44,47 @@ def test_chain_step_equals_the_step_of_separate_launches():
         top2 = torch.topk(lb.view(-1), 2).values
         if float(top2[0] - top2[1]) > 2e-2 * float(lb.abs().max()):
             assert int(ta.item()) == int(tb.item())
-    # the cache rows the steps appended agree (v bit-exactly unless an fp16 rounding moved upstream)
+    # The cache rows the steps appended agree: bit-exactly in the first layer; further down an fp16
+    # rounding that moved upstream shows (the random model's residual stream has channels of
+    # magnitude 1e4, where one fp16 step is 8, and the norm in front of q/k/v divides by them)
     pos = a.pos
-    for La, Lb in zip(a.layers, b.layers):
-        va, vb = a.kv_rows(La, "vc", pos, pos + 1), b.kv_rows(Lb, "vc", pos, pos + 1)
-        assert (va.float() - vb.float()).abs().max() <= 3e-2
+    for i, (La, Lb) in enumerate(zip(a.layers, b.layers)):
+        va, vb = a.kv_rows(La, "vc", pos, pos + 1).float(), b.kv_rows(Lb, "vc", pos, pos + 1).float()
+        if i == 0:
+            assert torch.equal(va, vb)
+        assert (va - vb).norm() / vb.norm() <= 3e-2
+
+
+@pytest.mark.timeout(180)
+@pytest.mark.parametrize("n_heads,n_kv,ctx,positions", [
+    (8, 2, 256, (0, 1, 17, 100, 255)),        # groups of 4 heads, shares of a few positions
+    (16, 2, 256, (3, 130, 255)),              # groups of 8 heads
+    (16, 8, 4096, (5, 2000, 4095)),           # shares of more than one tile of 128 positions
+])
+def test_attention_stage_at_many_positions(n_heads, n_kv, ctx, positions):
+    """One layer, a random cache, one token at several positions: the chain's attention stage (K rows
+    into tensor-core fragments, fp16 weights, splits merged by the o projection) against the kernel
+    of the separate launches.  One layer keeps the comparison well conditioned: 2e-3 in relative L2."""
+    import dataclasses
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    from elutq_b200.decoder import PRESETS, TPDecoder
+    dev = torch.device("cuda", 0)
+    cfg = dataclasses.replace(PRESETS["tiny"], layers=1, n_heads=n_heads, n_kv=n_kv, ctx=ctx)
+    a = TPDecoder(cfg, dev, 0, 1, seed=5, chain=True)
+    b = TPDecoder(cfg, dev, 0, 1, seed=5, chain=False)
+    assert a.use_chain and not b.use_chain
+    for pos in positions:
+        a.position.fill_(pos)
+        b.position.fill_(pos)
+        a.step_eager(11)
+        b.step_eager(11)
+        torch.cuda.synchronize()
+        assert a.chain.status() == 0 and a.attn.status() == 0 and b.attn.status() == 0
+        xa, xb = a.hidden_after_step().float(), b.hidden_after_step().float()
+        assert (xa - xb).norm() / xb.norm() <= 2e-3, pos
+        for name in ("kc", "vc"):
+            assert torch.equal(a.kv_rows(a.layers[0], name, pos, pos + 1), b.kv_rows(b.layers[0], name, pos, pos + 1))
 
 
 @pytest.mark.timeout(120)
@@ -59,7 +95,8 @@ def test_chain_in_a_graph_generates_the_same_tokens():
     assert a.chain.status() == 0
     assert ta == tb and len(ta) == 6
     for La, Lb in zip(a.layers, b.layers):
-        assert (a.kv_rows(La, "kc", 100, 106).float() - b.kv_rows(Lb, "kc", 100, 106).float()).abs().max() <= 3e-2
+        ka, kb = a.kv_rows(La, "kc", 100, 106).float(), b.kv_rows(Lb, "kc", 100, 106).float()
+        assert (ka - kb).norm() / kb.norm() <= 3e-2
         assert torch.equal(a.kv_rows(La, "kc", 106, 256), b.kv_rows(Lb, "kc", 106, 256))
 
 
