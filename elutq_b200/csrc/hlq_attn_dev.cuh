@@ -572,23 +572,26 @@ __device__ __forceinline__ void attention_partial_unit(const AttnArgs &a, int hk
     // warps w + 8 hand their half of the positions to warps w
     if (warp >= 8) *(float4 *)&sm.red[warp - 8][lane][0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     sync();
-    // this split's partial: a share without positions (t0 >= t1) publishes max = -inf, sum = 0
-    float *mine = a.partial + ((size_t)hk * nsplit + split) * G * (D + 2);
+    // This split's partial: outputs [head][split][D] (a head's splits lie side by side, every row a
+    // whole number of 128-byte lines), then the (max, sum) pairs [head][split][2].  A share without
+    // positions (t0 >= t1) publishes max = -inf, sum = 0.
     if (warp < 8) {
         const float4 o = *(const float4 *)&sm.red[warp][lane][0];
         const int d0 = 16 * warp + gid;
+        float *mine = a.partial + ((size_t)(hk * G) * nsplit + split) * D + d0;
+        const size_t hs = (size_t)nsplit * D;
         if (2 * tig < G) {
-            mine[(size_t)(2 * tig) * (D + 2) + d0] = acc[0] + o.x;
-            mine[(size_t)(2 * tig) * (D + 2) + d0 + 8] = acc[2] + o.z;
+            mine[(size_t)(2 * tig) * hs] = acc[0] + o.x;
+            mine[(size_t)(2 * tig) * hs + 8] = acc[2] + o.z;
         }
         if (2 * tig + 1 < G) {
-            mine[(size_t)(2 * tig + 1) * (D + 2) + d0] = acc[1] + o.y;
-            mine[(size_t)(2 * tig + 1) * (D + 2) + d0 + 8] = acc[3] + o.w;
+            mine[(size_t)(2 * tig + 1) * hs] = acc[1] + o.y;
+            mine[(size_t)(2 * tig + 1) * hs + 8] = acc[3] + o.w;
         }
     } else if (tid - 256 < G) {
         const int g = tid - 256;
-        mine[(size_t)g * (D + 2) + D] = sm.m_run[g];
-        mine[(size_t)g * (D + 2) + D + 1] = sm.l_run[g];
+        float2 *ml = (float2 *)(a.partial + (size_t)a.head_q * nsplit * D) + (size_t)(hk * G + g) * nsplit + split;
+        *ml = make_float2(sm.m_run[g], sm.l_run[g]);
     }
     mark(4);
 }
@@ -599,35 +602,27 @@ __device__ __forceinline__ void attention_partial_unit(const AttnArgs &a, int hk
 //   2. warp h (h < nheads) turns the splits' (max, sum) pairs of head h into normalized weights
 //      exp(max_s - max) / sum_s(...) in shared memory `wn` [4][64];
 //   3. after `sync`, out = sum_s output_s * weight_s.
-// `first_head` = local index of the first head, `partial` = [head_kv][nsplit][group][D + 2] floats.
-// Returns the merged value of thread `tid`'s channel (0 for tid >= 128 * nheads).  nsplit <= 64.
+// `first_head` = index of the first head, `partial` = [head][nsplit][D] floats, `ml` = [head][nsplit][2]
+// (as attention_partial_unit writes them).  Returns the merged value of thread `tid`'s channel (0
+// for tid >= 128 * nheads).  nsplit <= 64.
 template <int D, typename Sync>
-__device__ __forceinline__ float attention_merge_heads(const float *partial, int group, int nsplit, int first_head,
+__device__ __forceinline__ float attention_merge_heads(const float *partial, const float *ml, int nsplit, int first_head,
                                                        int nheads, int tid, float *wn, Sync sync) {
     const int lane = tid & 31, warp = tid >> 5;
     const int hl = tid / D, ch = tid % D;                       // head of this thread's channel
     const bool live = hl < nheads;
-    const int h = first_head + (live ? hl : 0), hk = h / group, g = h - hk * group;
-    const float *base = partial + ((size_t)hk * nsplit * group + g) * (D + 2);
-    const size_t stride = (size_t)group * (D + 2);
+    const float *base = partial + (size_t)(first_head + (live ? hl : 0)) * nsplit * D + ch;
     float ov[16];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) ov[u] = (live && u < nsplit) ? __ldcg(base + (size_t)u * stride + ch) : 0.f;
+    for (int u = 0; u < 16; ++u) ov[u] = (live && u < nsplit) ? __ldcg(base + (size_t)u * D) : 0.f;
     if (warp < nheads) {
-        const int hh = first_head + warp, hk2 = hh / group, g2 = hh - hk2 * group;
-        const float *b2 = partial + ((size_t)hk2 * nsplit * group + g2) * (D + 2);
-        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-        if (lane < nsplit) {
-            m0 = __ldcg(b2 + (size_t)lane * stride + D);
-            l0 = __ldcg(b2 + (size_t)lane * stride + D + 1);
-        }
-        if (lane + 32 < nsplit) {
-            m1 = __ldcg(b2 + (size_t)(lane + 32) * stride + D);
-            l1 = __ldcg(b2 + (size_t)(lane + 32) * stride + D + 1);
-        }
-        const float M = warp_max(fmaxf(m0, m1));
-        const float w0 = m0 > -INFINITY ? expf(m0 - M) : 0.f, w1 = m1 > -INFINITY ? expf(m1 - M) : 0.f;
-        const float den = warp_sum(l0 * w0 + l1 * w1);
+        const float2 *b2 = (const float2 *)ml + (size_t)(first_head + warp) * nsplit;
+        float2 p0 = make_float2(-INFINITY, 0.f), p1 = make_float2(-INFINITY, 0.f);
+        if (lane < nsplit) p0 = __ldcg(b2 + lane);
+        if (lane + 32 < nsplit) p1 = __ldcg(b2 + lane + 32);
+        const float M = warp_max(fmaxf(p0.x, p1.x));
+        const float w0 = p0.x > -INFINITY ? expf(p0.x - M) : 0.f, w1 = p1.x > -INFINITY ? expf(p1.x - M) : 0.f;
+        const float den = warp_sum(p0.y * w0 + p1.y * w1);
         wn[warp * 64 + lane] = w0 / den;
         wn[warp * 64 + lane + 32] = w1 / den;
     }
@@ -639,7 +634,7 @@ __device__ __forceinline__ float attention_merge_heads(const float *partial, int
         for (int s0 = 16; s0 < nsplit; s0 += 16) {
 #pragma unroll
             for (int u = 0; u < 16; ++u)
-                if (s0 + u < nsplit) out += __ldcg(base + (size_t)(s0 + u) * stride + ch) * wn[hl * 64 + s0 + u];
+                if (s0 + u < nsplit) out += __ldcg(base + (size_t)(s0 + u) * D) * wn[hl * 64 + s0 + u];
         }
     }
     return out;

@@ -67,7 +67,7 @@ struct ChainJob {
     const uint16_t *bias;
     float *acc;              // [np] fp32 accumulators, zero between uses
     const uint16_t *x;       // fp16 [k]: the activations (PLAIN) or the residual stream (NORM); ATTENTION: the
-                             // splits' partials of the attention stage before (float [head_kv][nsplit][group][130])
+                             // splits' partials of the attention stage before (float [head][nsplit][128], then [head][nsplit][2])
     __half *y;               // STORE: [n]; RESIDUAL: the residual stream [n], updated in place; GATED_SILU: [n / 2]
     const uint16_t *gamma;   // NORM: fp16 [k]
     const float *ss_in;      // NORM: sum of squares of the residual stream
@@ -76,6 +76,7 @@ struct ChainJob {
     int n, k, np, slices, duos, blocks;
     int in_kind, out_kind;
     int attn_nsplit, attn_group;   // ATTENTION input: splits per kv head, query heads per kv head
+    int attn_heads;                // ATTENTION input: query heads of the attention stage
 };
 
 struct ChainStage {
@@ -120,7 +121,7 @@ struct __align__(16) ChainItem {
     const float *ss_in;
     float *ss_out, *acc;
     __half *y;
-    void *unused_;
+    const float *attn_ml;    // SEGMENT with ATTENTION input: the splits' (max, sum) pairs, [head][split][2]
     float eps, inv_k;
     int n, job_slices, in_kind, out_kind;
     int kind, stage;
@@ -288,10 +289,12 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
                 // a slice of 512 channels = up to four heads of 128; the weights of the splits are
                 // formed once per head (in the group-sum area, free until the tables are built)
                 const float val = attention_merge_heads<128>(
-                    partial, it.attn, it.nsplit, it.slice * (kSliceK / 128), (it.valid + 127) / 128, tid,
+                    partial, it.attn_ml, it.nsplit, it.slice * (kSliceK / 128), (it.valid + 127) / 128, tid,
                     (float *)(aux + kChAuxMerge), [] { named_bar_sync<kChBarConsumers, kChConsumers>(); });
+                if (tid == 0) stamp(i, 10);
                 xw[tid] = __half_as_ushort(__float2half_rn(val));
                 named_bar_sync<kChBarConsumers, kChConsumers>();
+                if (tid == 0) stamp(i, 15);
             }
             const bool norm = cur_norm;
             const float inv_rms = norm ? ((const float *)(aux + kChAuxInvRms))[slot] : 1.f;
@@ -896,6 +899,7 @@ int hlq_chain_add_linears(hlq_chain *c, int count, const hlq_chain_linear *m, hl
             j.x = (const uint16_t *)at.partial;
             j.attn_nsplit = c->stages.back().nsplit;
             j.attn_group = at.group;
+            j.attn_heads = at.head_q;
         }
         j.y = (__half *)m[i].d_y;
         j.gamma = (const uint16_t *)m[i].d_gamma;
@@ -1024,6 +1028,8 @@ static void chain_build_items(const hlq_chain *c, int ctas, int q, int gpw, std:
                 it.n = jb.n; it.job_slices = jb.slices; it.in_kind = jb.in_kind; it.out_kind = jb.out_kind;
                 it.duo_a = da; it.duo_b = db; it.slice = p.slice;
                 it.nsplit = jb.attn_nsplit; it.attn = jb.attn_group;     // ATTENTION input: splits, heads per kv head
+                it.attn_ml = jb.in_kind == HLQ_CHAIN_IN_ATTENTION
+                                 ? (const float *)jb.x + (size_t)jb.attn_heads * jb.attn_nsplit * 128 : nullptr;
                 it.valid = jb.k - p.slice * kSliceK < kSliceK ? jb.k - p.slice * kSliceK : kSliceK;
                 return it;
             };
