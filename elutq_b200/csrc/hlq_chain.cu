@@ -35,6 +35,8 @@
 #include <atomic>
 #include <mutex>
 #include <new>
+#include <algorithm>
+#include <utility>
 #include <vector>
 
 #include "hlq_attn_dev.cuh"
@@ -1062,16 +1064,65 @@ static void chain_build_items(const hlq_chain *c, int ctas, int q, int gpw, std:
                     share[best] += used < ctas ? 1 : -1;
                     used += used < ctas ? 1 : -1;
                 }
+                // What that costs: the largest share plus one set of tables (in duos: building the 64
+                // tables of a slice takes as long as streaming kTableDuos duos).  Where whole CTAs per
+                // pair fit badly (56 slices on 148 CTAs: 2 or 3 CTAs per slice, 256 or 171 duos each)
+                // it is cheaper to cut the pairs' concatenated duos into `ctas` runs of equal COST and
+                // let the CTAs whose run crosses a slice build two sets of tables: the smallest budget
+                // per CTA for which that fits is found by bisection.
+                constexpr int kTableDuos = 36;
+                long long whole_cost = 0;
+                for (int p = 0; p < np; ++p) {
+                    const long long cst = (pairs[p].duos + share[p] - 1) / share[p] + kTableDuos;
+                    if (cst > whole_cost) whole_cost = cst;
+                }
+                auto fits = [&](long long budget, std::vector<std::vector<std::pair<int, std::pair<int, int>>>> *runs) {
+                    int g = 0, p = 0, at = 0;          // CTA, pair, first duo of the pair not yet dealt out
+                    if (runs) runs->assign(ctas, {});
+                    while (p < np) {
+                        if (g >= ctas) return false;
+                        long long left = budget;
+                        while (p < np && left > kTableDuos) {
+                            left -= kTableDuos;
+                            const int d = (int)std::min<long long>(pairs[p].duos - at, left);
+                            if (runs) (*runs)[g].push_back({p, {at, at + d}});
+                            left -= d;
+                            at += d;
+                            if (at < pairs[p].duos) break;       // the CTA is full
+                            ++p;
+                            at = 0;
+                        }
+                        ++g;
+                    }
+                    return true;
+                };
+                long long lo = total / ctas + kTableDuos, hi = whole_cost;      // lo may not fit, hi is tried below
+                bool cut_fits = fits(hi, nullptr);
+                if (cut_fits) {
+                    while (lo < hi) {
+                        const long long mid = (lo + hi) / 2;
+                        if (fits(mid, nullptr)) hi = mid; else lo = mid + 1;
+                    }
+                }
                 // the stages start their dealing at different CTAs, so that the CTAs that draw
                 // the slightly larger shares change from stage to stage
                 int g = (int)((si * 37) % ctas);
-                for (int p = 0; p < np; ++p)
-                    for (int t = 0; t < share[p]; ++t) {
-                        const int da = (int)((long long)pairs[p].duos * t / share[p]);
-                        const int db = (int)((long long)pairs[p].duos * (t + 1) / share[p]);
-                        if (db > da) out[g].push_back(segment(pairs[p], da, db));
+                if (cut_fits && hi + 2 < whole_cost) {
+                    std::vector<std::vector<std::pair<int, std::pair<int, int>>>> runs;
+                    fits(hi, &runs);
+                    for (int t = 0; t < ctas; ++t) {
+                        for (const auto &r : runs[t]) out[g].push_back(segment(pairs[r.first], r.second.first, r.second.second));
                         g = (g + 1) % ctas;
                     }
+                } else {
+                    for (int p = 0; p < np; ++p)
+                        for (int t = 0; t < share[p]; ++t) {
+                            const int da = (int)((long long)pairs[p].duos * t / share[p]);
+                            const int db = (int)((long long)pairs[p].duos * (t + 1) / share[p]);
+                            if (db > da) out[g].push_back(segment(pairs[p], da, db));
+                            g = (g + 1) % ctas;
+                        }
+                }
             } else {
                 long long cum = 0;
                 for (int p = 0; p < np; ++p) {
