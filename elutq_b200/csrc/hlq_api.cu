@@ -9,6 +9,7 @@
 #include <new>
 #include <vector>
 
+#include "hlq_gemv_args.cuh"
 #include "hlq_internal.h"
 
 namespace hlq {
@@ -100,6 +101,9 @@ static void free_buffers(hlq_weight *w) {
     if (w->d_bias) cudaFree(w->d_bias);
     if (w->d_status) cudaFree(w->d_status);
     w->d_status = nullptr;
+    if (w->d_codes) cudaFree(w->d_codes);
+    w->d_codes = nullptr;
+    w->codes_bytes = 0;
     free_sparse(w);
     w->d_planes = nullptr;
     w->d_meta = nullptr;
@@ -297,7 +301,7 @@ int hlq_weight_get_info(const hlq_weight *w, hlq_weight_info *info) {
     info->shard_mode = w->shard_mode;
     info->full_in_channel = w->k_full;
     info->full_out_channel = w->n_full;
-    info->device_bytes = w->planes_bytes + w->meta_bytes + (w->d_bias ? (int64_t)w->n * 2 : 0);
+    info->device_bytes = w->planes_bytes + w->meta_bytes + w->codes_bytes + (w->d_bias ? (int64_t)w->n * 2 : 0);
     info->algorithmic_bytes = (int64_t)w->q * w->n * (w->k / 8) + 2 * (int64_t)(w->q + 1) * w->n * (w->k / w->g);
     return HLQ_OK;
 }
@@ -310,6 +314,27 @@ int hlq_weight_buffers(const hlq_weight *w, void **d_planes, int64_t *planes_byt
     if (d_meta) *d_meta = w->d_meta;
     if (meta_bytes) *meta_bytes = w->meta_bytes;
     if (d_bias) *d_bias = w->d_bias;
+    return HLQ_OK;
+}
+
+int hlq_weight_build_batch_codes(hlq_weight *w, void *stream) {
+    if (!w) return HLQ_ERR_INVALID_ARGUMENT;
+    if (w->layout != HLQ_LAYOUT_STREAM || (w->q != 2 && w->q != 3)) return HLQ_ERR_UNSUPPORTED;
+    if (w->d_codes) return HLQ_OK;
+    int cur = -1;
+    HLQ_CUDA(cudaGetDevice(&cur));
+    if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;
+    const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
+    const int64_t bytes = (int64_t)d.slices * d.duos * hlq::kCodeDuoBytes;
+    uint8_t *p = nullptr;
+    HLQ_CUDA(cudaMalloc((void **)&p, (size_t)bytes));
+    const int rc = hlq::launch_build_codes(w->q, w->d_planes, p, d.slices, d.duos, (cudaStream_t)stream);
+    if (rc) {
+        cudaFree(p);
+        return rc;
+    }
+    w->d_codes = p;
+    w->codes_bytes = bytes;
     return HLQ_OK;
 }
 

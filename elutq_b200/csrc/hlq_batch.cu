@@ -141,11 +141,11 @@ struct ByteTables {
     uint32_t lo[2], hi[2];
 };
 template <int Q, int GPW>
-__device__ __forceinline__ void build_tables(const Tile<Q, GPW> &t, int ou, int u, ByteTables<Q> &bt) {
-    const float z = tile_meta<GPW>(t.mt[Q], ou, u);
+__device__ __forceinline__ void build_tables(const uint32_t (&mt)[Q + 1][GPW], int ou, int u, ByteTables<Q> &bt) {
+    const float z = tile_meta<GPW>(mt[Q], ou, u);
     float al[Q];
 #pragma unroll
-    for (int p = 0; p < Q; ++p) al[p] = tile_meta<GPW>(t.mt[p], ou, u);
+    for (int p = 0; p < Q; ++p) al[p] = tile_meta<GPW>(mt[p], ou, u);
     float v[1 << Q];
     v[0] = z;
 #pragma unroll
@@ -169,17 +169,76 @@ __device__ __forceinline__ void build_tables(const Tile<Q, GPW> &t, int ou, int 
     }
 }
 
-// One duo (16 rows x the slice's 512 channels) times the rows of x in shared memory.
-// `bs`: this lane's base into the fragment-ordered activations (its row of x and quarter).
-template <int Q, int GPW, int NT>
-__device__ __forceinline__ void mma_tile(const Tile<Q, GPW> &t, uint32_t bs, int r, uint32_t usel,
-                                         float (&acc)[4 / NT][NT][4]) {
-    constexpr int kChains = 4 / NT;     // independent accumulators per block of 8 rows of x
-    uint32_t pw[2][Q][4];
+// What the consumers hold of one duo: the planes as they are stored, or (CODES) the code words -
+// per lane rows r and r + 8, word (c, s) = eight nibbles, nibble i the q bits of channel
+// 32 c + 4 i + s of the lane's quarter (planes 0.. from the low bit) - plus the scales and zeros.
+template <int Q, int GPW, bool CODES>
+struct BatchTile {
+    uint4 w[2][CODES ? 4 : Q];      // planes: [oct][plane]; codes: [oct][word c] = {s = 0, 1, 2, 3}
+    uint32_t mt[Q + 1][GPW];
+};
+template <int Q, int GPW, bool CODES>
+__device__ __forceinline__ void load_batch_tile(BatchTile<Q, GPW, CODES> &t, const uint8_t *pl, const uint16_t *mp) {
+    constexpr int W = CODES ? 4 : Q;
 #pragma unroll
     for (int ou = 0; ou < 2; ++ou)
 #pragma unroll
-        for (int p = 0; p < Q; ++p) source_order(t.w[ou][p], r & 4, usel, pw[ou][p]);
+        for (int p = 0; p < W; ++p) t.w[ou][p] = ldg_stream_v4(pl + (ou * W + p) * kCellBytes);
+#pragma unroll
+    for (int pp = 0; pp <= Q; ++pp) {
+        const uint16_t *m = mp + pp * (32 * 2 * GPW);
+        if (GPW == 1) {
+            t.mt[pp][0] = ldg_stream_u32(m);
+        } else if (GPW == 2) {
+            const uint2 v = ldg_stream_v2(m);
+            t.mt[pp][0] = v.x;
+            t.mt[pp][GPW - 1] = v.y;
+        } else {
+            const uint4 v = ldg_stream_v4(m);
+            t.mt[pp][0] = v.x;
+            t.mt[pp][1 % GPW] = v.y;
+            t.mt[pp][2 % GPW] = v.z;
+            t.mt[pp][3 % GPW] = v.w;
+        }
+    }
+}
+
+// The code words of word c of a lane's rows from its planes in source order: xs[oct][s].
+template <int Q>
+__device__ __forceinline__ void code_words(const uint32_t (&pw)[2][Q][4], int c, uint32_t (&xs)[2][4]) {
+    // planes 1 and 2 rotated (not shifted: the top nibble's bits wrap and come back) so that
+    // bit p of plane 0, bit p + 1 of plane 1', bit p + 2 of plane 2' belong to one channel
+#pragma unroll
+    for (int ou = 0; ou < 2; ++ou) {
+        const uint32_t w0 = pw[ou][0][c];
+        const uint32_t w1 = __funnelshift_l(pw[ou][1 % Q][c], pw[ou][1 % Q][c], 1);
+        const uint32_t w2 = __funnelshift_l(pw[ou][2 % Q][c], pw[ou][2 % Q][c], 2);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            constexpr uint32_t kOne = 0x11111111u, kTwo = 0x33333333u;
+            const uint32_t m1 = s ? ((kOne << s) | (kOne >> (32 - s))) : kOne;
+            const uint32_t m2 = s ? ((kTwo << s) | (kTwo >> (32 - s))) : kTwo;
+            uint32_t m = merge_bits(w0, w1, m1);
+            if (Q == 3) m = merge_bits(m, w2, m2);
+            if (s) m = __funnelshift_r(m, m, s);
+            xs[ou][s] = m & (Q == 3 ? 0x77777777u : 0x33333333u);
+        }
+    }
+}
+
+// One duo (16 rows x the slice's 512 channels) times the rows of x in shared memory.
+// `bs`: this lane's base into the fragment-ordered activations (its row of x and quarter).
+template <int Q, int GPW, int NT, bool CODES>
+__device__ __forceinline__ void mma_tile(const BatchTile<Q, GPW, CODES> &t, uint32_t bs, int r, uint32_t usel,
+                                         float (&acc)[4 / NT][NT][4]) {
+    constexpr int kChains = 4 / NT;     // independent accumulators per block of 8 rows of x
+    uint32_t pw[2][Q][4];
+    if constexpr (!CODES) {
+#pragma unroll
+        for (int ou = 0; ou < 2; ++ou)
+#pragma unroll
+            for (int p = 0; p < Q; ++p) source_order(t.w[ou][p], r & 4, usel, pw[ou][p]);
+    }
     constexpr int kWordsPerGroup = 4 / GPW;
     constexpr int gshift = GPW == 1 ? 3 : (GPW == 2 ? 2 : 1);
     ByteTables<Q> bt[2];
@@ -189,37 +248,25 @@ __device__ __forceinline__ void mma_tile(const Tile<Q, GPW> &t, uint32_t bs, int
             // source group c / kWordsPerGroup sits at positional sub-group (that) ^ (r >> gshift)
             const int u = (c / kWordsPerGroup) ^ ((r >> gshift) & (GPW - 1));
 #pragma unroll
-            for (int ou = 0; ou < 2; ++ou) build_tables<Q, GPW>(t, ou, u, bt[ou]);
+            for (int ou = 0; ou < 2; ++ou) build_tables<Q, GPW>(t.mt, ou, u, bt[ou]);
         }
-        // planes 1 and 2 rotated (not shifted: the top nibble's bits wrap and come back) so that
-        // bit p of plane 0, bit p + 1 of plane 1', bit p + 2 of plane 2' belong to one channel
-        uint32_t w0[2], w1[2], w2[2];
+        uint32_t xs[2][4];       // nibble i of xs[oct][s]: the code of channel 4 * i + s of this word
+        if constexpr (CODES) {
 #pragma unroll
-        for (int ou = 0; ou < 2; ++ou) {
-            w0[ou] = pw[ou][0][c];
-            w1[ou] = __funnelshift_l(pw[ou][1 % Q][c], pw[ou][1 % Q][c], 1);
-            w2[ou] = __funnelshift_l(pw[ou][2 % Q][c], pw[ou][2 % Q][c], 2);
+            for (int ou = 0; ou < 2; ++ou) {
+                xs[ou][0] = t.w[ou][c].x; xs[ou][1] = t.w[ou][c].y; xs[ou][2] = t.w[ou][c].z; xs[ou][3] = t.w[ou][c].w;
+            }
+        } else {
+            code_words<Q>(pw, c, xs);
         }
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-            // nibble i of xsel: the code of channel 4 * i + s of this word
-            constexpr uint32_t kOne = 0x11111111u, kTwo = 0x33333333u;
-            const uint32_t m1 = s ? ((kOne << s) | (kOne >> (32 - s))) : kOne;
-            const uint32_t m2 = s ? ((kTwo << s) | (kTwo >> (32 - s))) : kTwo;
-            uint32_t xsel[2];
-#pragma unroll
-            for (int ou = 0; ou < 2; ++ou) {
-                uint32_t m = merge_bits(w0[ou], w1[ou], m1);
-                if (Q == 3) m = merge_bits(m, w2[ou], m2);
-                if (s) m = __funnelshift_r(m, m, s);
-                xsel[ou] = m & (Q == 3 ? 0x77777777u : 0x33333333u);
-            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 uint32_t a[2][2];
 #pragma unroll
                 for (int ou = 0; ou < 2; ++ou) {
-                    const uint32_t sel = h ? (xsel[ou] >> 16) : xsel[ou];
+                    const uint32_t sel = h ? (xs[ou][s] >> 16) : xs[ou][s];
                     const uint32_t lb = prmt(bt[ou].lo[0], bt[ou].lo[1], sel);
                     const uint32_t hb = prmt(bt[ou].hi[0], bt[ou].hi[1], sel);
                     a[ou][0] = prmt(lb, hb, 0x5140u);    // channels 4 * (4h) + s, 4 * (4h + 1) + s
@@ -237,6 +284,31 @@ __device__ __forceinline__ void mma_tile(const Tile<Q, GPW> &t, uint32_t bs, int
     }
 }
 
+// Writes the code words of a weight from its planes: one warp per duo.
+template <int Q>
+__global__ void __launch_bounds__(256) build_codes_kernel(const uint8_t *__restrict__ planes, uint8_t *__restrict__ codes,
+                                                          long long nduos) {
+    const int lane = threadIdx.x & 31, r = lane >> 2;
+    const long long d = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (d >= nduos) return;
+    const uint32_t usel = unpermute_selector(r);
+    const uint8_t *pl = planes + d * (2 * Q * kCellBytes) + lane * 16;
+    uint32_t pw[2][Q][4];
+#pragma unroll
+    for (int ou = 0; ou < 2; ++ou)
+#pragma unroll
+        for (int p = 0; p < Q; ++p) source_order(*(const uint4 *)(pl + (ou * Q + p) * kCellBytes), r & 4, usel, pw[ou][p]);
+    uint8_t *out = codes + d * kCodeDuoBytes + lane * 16;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t xs[2][4];
+        code_words<Q>(pw, c, xs);
+#pragma unroll
+        for (int ou = 0; ou < 2; ++ou)
+            *(uint4 *)(out + (ou * 4 + c) * kCellBytes) = make_uint4(xs[ou][0], xs[ou][1], xs[ou][2], xs[ou][3]);
+    }
+}
+
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -244,7 +316,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
 
-template <int Q, int GPW, int NT>
+template <int Q, int GPW, int NT, bool CODES>
 __global__ void __launch_bounds__(kBmThreads, 1) batch_mma_kernel(const __grid_constant__ GemvArgs a) {
     static_assert(Q == 2 || Q == 3, "byte tables hold at most eight codes");
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -428,19 +500,19 @@ __global__ void __launch_bounds__(kBmThreads, 1) batch_mma_kernel(const __grid_c
 
     // =============================== consumer warps =======================================
     const int r = lane >> 2, j = lane & 3;
-    constexpr long long kDuoPlaneBytes = 2 * Q * kCellBytes;
+    constexpr long long kDuoPlaneBytes = CODES ? kCodeDuoBytes : 2 * Q * kCellBytes;
     constexpr long long kDuoMetaElems = (Q + 1) * 32 * 2 * GPW;
     // B fragments: lane (r, j) reads row of x (r + 8 nt), quarter j
     const uint32_t bs0 = sbase + kBmB + (uint32_t)r * kBmRowStride + (uint32_t)j * kBmQuarterStride;
     const uint32_t usel = unpermute_selector(r);
 
-    Tile<Q, GPW> t0, t1;
-    const uint8_t *planes;
+    BatchTile<Q, GPW, CODES> t0, t1;
+    const uint8_t *planes;        // the planes, or the code words
     const uint16_t *meta;
     float *accb;
     int cur, dend;
-    auto load_duo = [&](Tile<Q, GPW> &t, int d) {
-        load_tile<Q, GPW>(t, planes + (long long)d * kDuoPlaneBytes, meta + (long long)d * kDuoMetaElems);
+    auto load_duo = [&](BatchTile<Q, GPW, CODES> &t, int d) {
+        load_batch_tile<Q, GPW, CODES>(t, planes + (long long)d * kDuoPlaneBytes, meta + (long long)d * kDuoMetaElems);
     };
     // the next duo of the segment that nobody has taken yet
     auto take = [&](int slot) {
@@ -451,7 +523,7 @@ __global__ void __launch_bounds__(kBmThreads, 1) batch_mma_kernel(const __grid_c
     auto open_segment = [&](const Seg &sg) {
         cur = sg.duo_a + warp;
         dend = sg.duo_b;
-        planes = sg.planes - (long long)sg.duo_a * kDuoPlaneBytes + lane * 16;
+        planes = (CODES ? sg.codes : sg.planes) - (long long)sg.duo_a * kDuoPlaneBytes + lane * 16;
         meta = sg.meta - (long long)sg.duo_a * kDuoMetaElems + lane * (2 * GPW);
         // reduction target of this lane: even j: row r, odd j: row r + 8; rows of x 4 (j >> 1) ..
         accb = sg.acc + (long long)(r + ((j & 1) ? 8 : 0)) * MT + 4 * (j >> 1);
@@ -462,9 +534,9 @@ __global__ void __launch_bounds__(kBmThreads, 1) batch_mma_kernel(const __grid_c
         if (!have || !ring[0].live) return;
         open_segment(ring[0]);
     }
-    auto run_tile = [&](const Tile<Q, GPW> &t, int d, uint32_t bs) {
+    auto run_tile = [&](const BatchTile<Q, GPW, CODES> &t, int d, uint32_t bs) {
         float accs[4 / NT][NT][4] = {};
-        mma_tile<Q, GPW, NT>(t, bs, r, usel, accs);
+        mma_tile<Q, GPW, NT, CODES>(t, bs, r, usel, accs);
         float acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -514,12 +586,12 @@ __global__ void __launch_bounds__(kBmThreads, 1) batch_mma_kernel(const __grid_c
     }
 }
 
-template <int Q, int GPW, int NT>
+template <int Q, int GPW, int NT, bool CODES>
 int launch_inst(const GemvArgs &args, int ctas, cudaStream_t stream) {
     static std::atomic<bool> configured[64];
     int dev = 0;
     HLQ_CUDA(cudaGetDevice(&dev));
-    auto kernel = batch_mma_kernel<Q, GPW, NT>;
+    auto kernel = batch_mma_kernel<Q, GPW, NT, CODES>;
     if (!configured[dev & 63].load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_first_use);
         HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBmSmem));
@@ -545,13 +617,28 @@ int launch_batch_mma(int q, int gpw, const GemvArgs &a_in, int ctas, int m, cuda
     a.chunk_duos = kChunkDuos;
     a.seg_cost = kChunkSegCost;
     a.total_units = a_in.total_units_chunked;
-#define HLQ_CASE(QV, GV)                                                         \
-    if (q == QV && gpw == GV)                                                    \
-        return m <= 8 ? launch_inst<QV, GV, 1>(a, ctas, stream) : launch_inst<QV, GV, 2>(a, ctas, stream);
+#define HLQ_CASE(QV, GV)                                                                                       \
+    if (q == QV && gpw == GV) {                                                                                \
+        if (a.use_codes)                                                                                       \
+            return m <= 8 ? launch_inst<QV, GV, 1, true>(a, ctas, stream) : launch_inst<QV, GV, 2, true>(a, ctas, stream); \
+        return m <= 8 ? launch_inst<QV, GV, 1, false>(a, ctas, stream) : launch_inst<QV, GV, 2, false>(a, ctas, stream);   \
+    }
     HLQ_CASE(2, 1) HLQ_CASE(2, 2) HLQ_CASE(2, 4)
     HLQ_CASE(3, 1) HLQ_CASE(3, 2) HLQ_CASE(3, 4)
 #undef HLQ_CASE
     return HLQ_ERR_SHAPE;
+}
+
+int launch_build_codes(int q, const uint8_t *planes, uint8_t *codes, int slices, int duos, cudaStream_t stream) {
+    const long long nduos = (long long)slices * duos;
+    if (nduos <= 0) return HLQ_OK;
+    const unsigned grid = (unsigned)((nduos + 7) / 8);
+    if (q == 2) build_codes_kernel<2><<<grid, 256, 0, stream>>>(planes, codes, nduos);
+    else if (q == 3) build_codes_kernel<3><<<grid, 256, 0, stream>>>(planes, codes, nduos);
+    else return HLQ_ERR_UNSUPPORTED;
+    HLQ_CUDA(cudaGetLastError());
+    count_launch();
+    return HLQ_OK;
 }
 
 }  // namespace hlq

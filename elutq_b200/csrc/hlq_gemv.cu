@@ -813,6 +813,7 @@ static void fill_job(Job &j, const hlq_weight *w, const StreamDims &d, const voi
                      void *y, int y_dtype, float *partial, unsigned *counters, long long unit_begin) {
     j.planes = w->d_planes;
     j.meta = w->d_meta;
+    j.codes = w->d_codes;
     j.bias = w->d_bias;
     j.acc = partial;
     j.counters = counters;
@@ -878,6 +879,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         a.dyn_smem = kLut8DynSmem;
         a.spin_limit = kDefaultSpinLimit;
         a.y_is_f32 = y_dtype == HLQ_F32;
+        a.use_codes = w->d_codes != nullptr;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         rc = apply_input_op(a.single, op, x_dtype, m0);
@@ -957,6 +959,7 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         a.dyn_smem = kLut8DynSmem;
         a.spin_limit = kDefaultSpinLimit;
         a.y_is_f32 = y_dtype == HLQ_F32;
+        a.use_codes = w->d_codes != nullptr;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         int ctas = di->sms;
@@ -1183,6 +1186,7 @@ struct hlq_group {
     long long duo_units = 0;      // (slice, duo) pairs
     int seg_cost = 0;
     bool one_row_passes = false;  // a member has an input transform
+    bool use_codes = false;       // every member had code words when the group was made
     std::vector<const hlq_weight *> weights;
     std::vector<hlq::Job> jobs_host;
     hlq::Job *d_jobs = nullptr;
@@ -1252,6 +1256,8 @@ int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weight
         }
         g->total_units = ub;
         g->total_units_chunked = ubc;
+        g->use_codes = true;
+        for (int i = 0; i < count; ++i) g->use_codes = g->use_codes && weights[i]->d_codes != nullptr;
     }
     if (prev >= 0) cudaSetDevice(prev);
     if (rc) {
@@ -1311,6 +1317,7 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.njobs = g->count;
     a.total_units = g->total_units;
     a.total_units_chunked = g->total_units_chunked;
+    a.use_codes = g->use_codes;
     a.seg_cost = g->seg_cost;
     a.status = (int *)g->d_scratch;
     a.dyn_smem = kLut8DynSmem;

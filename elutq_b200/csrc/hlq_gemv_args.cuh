@@ -13,6 +13,7 @@ namespace hlq {
 struct Job {
     const uint8_t *planes;
     const uint16_t *meta;
+    const uint8_t *codes; // optional second copy of the planes as 4-bit code words (hlq_batch.cu), or nullptr
     const uint16_t *bias;
     float *acc;           // [m][np] fp32 accumulators, zero between launches
     unsigned *counters;   // [m][blocks]
@@ -47,6 +48,7 @@ struct GemvArgs {
     int one_row_passes;   // host only: a job has an input transform (one row of x per pass)
     int spin_limit;       // polls after which a bounded wait gives up
     int batch_rows;       // small-batch kernel: rows of x of the launch (all served by one pass)
+    int use_codes;        // small-batch kernel: every job of the launch has code words
     int chunk_duos;       // 0: a job's units run slice by slice over all its duos; else chunk by chunk of
                           // this many duos, all slices of a chunk before the next chunk (then total_units
                           // and the jobs' unit_begin_chunked count seg_cost per (slice, chunk))
@@ -56,6 +58,7 @@ struct GemvArgs {
 // Descriptor of one segment, written by the control warp into shared memory.
 struct Seg {
     const uint8_t *planes;  // first cell of the segment
+    const uint8_t *codes;   // first code words of the segment (jobs that have them), else nullptr
     const uint16_t *meta;   // first meta entry of the segment
     const uint16_t *bias;
     float *acc;             // accumulator row base of mrow
@@ -85,6 +88,7 @@ __host__ __device__ static inline long long launch_units(int slices, int duos, i
 // is done, so the completion work is spread over the CTAs instead of falling to whoever holds a
 // job's last slice.  Its segments cost little beside their duos.
 constexpr int kChunkDuos = 128;
+constexpr int kCodeDuoBytes = 4096;     // code words of one duo: 16 rows x 512 channels x 4 bits
 constexpr int kChunkSegCost = 4;
 __host__ __device__ static inline long long launch_units_chunked(int slices, int duos, int chunk, int seg_cost) {
     const int chunks = (duos + chunk - 1) / chunk;
@@ -170,6 +174,7 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     const int db = (int)((long long)(chunk_len - da) < left ? chunk_len : da + left);
     const long long cell = (long long)s * jb.duos + chunk_first + da;           // in duos
     sg.planes = jb.planes + cell * (2 * Q * kCellBytes);
+    sg.codes = jb.codes ? jb.codes + cell * kCodeDuoBytes : nullptr;
     sg.meta = jb.meta + cell * ((Q + 1) * 32 * 2 * GPW);
     sg.bias = jb.bias;
     sg.acc = jb.acc + (long long)w.mrow * jb.np;
@@ -191,6 +196,9 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
 // The small-batch kernel (hlq_batch.cu): whether it takes (q, m), and its launch over the jobs of `a`.
 bool batch_mma_supported(int q, int m);
 int launch_batch_mma(int q, int gpw, const GemvArgs &a, int ctas, int m, cudaStream_t stream);
+// The code words of a weight in the streaming layout (hlq_weight_build_batch_codes): device buffer of
+// slices * duos * kCodeDuoBytes bytes from its planes.
+int launch_build_codes(int q, const uint8_t *planes, uint8_t *codes, int slices, int duos, cudaStream_t stream);
 
 // ---- host helpers of the launchers ----------------------------------------------------------
 struct DeviceInfo {

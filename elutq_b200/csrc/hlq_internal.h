@@ -20,6 +20,10 @@ struct hlq_weight {
     uint16_t *d_meta = nullptr;
     uint16_t *d_bias = nullptr;
     int64_t planes_bytes = 0, meta_bytes = 0;
+    // optional (streaming layout, 2 or 3 bits): the planes once more as 4-bit code words per weight,
+    // which the small-batch kernel reads instead of the planes (hlq_weight_build_batch_codes)
+    uint8_t *d_codes = nullptr;
+    int64_t codes_bytes = 0;
     // HLQ_LAYOUT_EXPORT only: 256 zeroed bytes whose first word is the generic kernel's status
     // word when a forward call brings no workspace (allocated with the handle, never in a
     // launch path).

@@ -71,6 +71,19 @@ class HLQWeight:
                            "hlq_weight_set_sparse")
         return self
 
+    def build_batch_codes(self):
+        """Adds the second copy of the planes as 4-bit code words (2- and 3-bit weights in the streaming
+        layout; half a byte per weight of device memory): calls with 3..16 rows of activations read
+        them instead of the planes.  Call before the weight goes into an HLQGroup."""
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().hlq_weight_build_batch_codes(self.handle, _stream_ptr(self.device)),
+                       "hlq_weight_build_batch_codes")
+            torch.cuda.current_stream(self.device).synchronize()
+        info = _lib.WeightInfo()
+        _lib.check(_lib.lib().hlq_weight_get_info(self._h, ctypes.byref(info)), "hlq_weight_get_info")
+        self.info = info
+        return self
+
     def sparse_pairs(self) -> int:
         v = ctypes.c_int(0)
         _lib.check(_lib.lib().hlq_weight_sparse_pairs(self.handle, ctypes.byref(v)), "hlq_weight_sparse_pairs")

@@ -189,6 +189,14 @@ int hlq_weight_sparse_pairs(const hlq_weight *w, int *pairs);
 int hlq_weight_get_sparse(const hlq_weight *w, uint32_t *h_mask, uint8_t *h_blocks, uint16_t *h_scales,
                           void *stream);
 
+/* Optional: a second copy of the planes of a 2- or 3-bit weight in the streaming layout as one 4-bit
+ * code word per weight (the planes' bits of a weight side by side; n_pad * k_pad / 2 bytes of device
+ * memory, counted in hlq_weight_info.device_bytes).  Calls with 3..16 rows of activations then read
+ * the code words instead of the planes and skip the bit gathering that binds them (their results
+ * are the same numbers).  Build it before the weight is put into a group; it is freed with the
+ * handle and never exported.  No counterpart in the reference. */
+int hlq_weight_build_batch_codes(hlq_weight *w, void *stream);
+
 /* ---- forward ------------------------------------------------------------------------ */
 
 /* Bytes of device scratch hlq_linear_forward needs for this problem (0 is possible).

@@ -97,3 +97,45 @@ def test_group_launch_with_rows(L):
     for d, y in zip(ds, ys):
         ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], 128, d["bias"])
         assert O.normwise_error(y.float().cpu().numpy(), ref) <= TOL_F16
+
+
+@pytest.mark.parametrize("q", [2, 3])
+@pytest.mark.parametrize("g", [128, 64, 32])
+def test_code_words_give_the_same_numbers(L, q, g):
+    """The optional copy of the planes as 4-bit code words: same tables, same selectors, so the same
+    products up to the order of the fp32 additions; the handle reports the extra bytes."""
+    d = O.synth_linear(200, 1152, q, g, m=16, seed=7 * q + g, bias=True, signed_alpha=True)
+    plain = make(d, g, max_batch=16)
+    coded = make(d, g, max_batch=16)
+    before = coded.weight.info.device_bytes
+    coded.weight.build_batch_codes()
+    assert coded.weight.info.device_bytes - before == 224 * 1536 // 2      # n padded to 32, k to 512
+    ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
+    x = torch.from_numpy(d["x"]).cuda()
+    for m in (1, 2, 3, 5, 8, 11, 16):
+        ya, yb = forward(plain, x[:m]), forward(coded, x[:m])
+        assert O.normwise_error(yb, ref[:m]) <= TOL_F16, m
+        assert O.normwise_error(yb, ya) <= 2e-3, m      # one fp16 step of the output at most
+    # the export is unaffected
+    e0, e1 = plain.weight.to_export(), coded.weight.to_export()
+    assert np.array_equal(e0.w_quant, e1.w_quant) and np.array_equal(e0.w_scale, e1.w_scale)
+
+
+def test_code_words_in_a_group_at_llama_shapes(L):
+    from elutq_b200 import linear
+    shapes = [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)]
+    ds = [O.synth_linear(n, k, 3, 128, m=8, seed=90 + i) for i, (n, k) in enumerate(shapes)]
+    mods = [make(d, 128, max_batch=8) for d in ds]
+    for mod in mods:
+        mod.weight.build_batch_codes()
+    group = linear.HLQGroup([m.weight for m in mods], max_m=8)
+    xs = [torch.from_numpy(d["x"]).cuda() for d in ds]
+    ys = [torch.empty((8, n), dtype=torch.float16, device="cuda") for n, _ in shapes]
+    group.bind(xs, ys)
+    for _ in range(2):
+        group.forward(8)
+    torch.cuda.synchronize()
+    assert group.kernel_status() == 0
+    for d, y in zip(ds, ys):
+        ref = O.hlq_linear(d["x"].astype(np.float32), d["w_quant"], d["w_scale"], d["w_zero"], 128, dtype=np.float32)
+        assert O.normwise_error(y.float().cpu().numpy(), ref) <= TOL_F16
