@@ -39,6 +39,7 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 NCU_TRAFFIC_RATIO = (130.33 + 3.70) / 129.50   # dram__bytes_read + write over algorithmic bytes (lut8_gemv_kernel)
+NCU_TRAFFIC_RATIO_CHAIN = (294.63 + 6.50) / 292.6   # the same for decode_chain_kernel (weights + KV cache of a 4-layer capture)
 HBM_NOMINAL_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 REPEATS = 5                                    # timed blocks of --steps steps; the median is reported
@@ -707,8 +708,8 @@ def run_decode(args):
         "pct_of_8tbs_per_gpu": 100.0 * my_bytes / sec / 1e9 / HBM_NOMINAL_GBS,
         "roofline": {"bound": "hbm", "achieved": my_bytes / sec / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": my_bytes / sec / 1e9 / peaks["hbm"],
-                     "traffic": NCU_TRAFFIC_RATIO * my_bytes / gemv_launches,
-                     "traffic_source": "ncu capture of a 2-layer launch of the kernel, scaled by algorithmic bytes",
+                     "traffic": (NCU_TRAFFIC_RATIO_CHAIN if dec.use_chain else NCU_TRAFFIC_RATIO) * my_bytes / gemv_launches,
+                     "traffic_source": "ncu capture of a 4-layer launch of the kernel (profiles/), scaled by algorithmic bytes",
                      "peak_source": f"of {peaks['kind']}",
                      "kernel": "decode_chain_kernel" if dec.use_chain else "lut8_gemv_kernel",
                      "launches_per_step": gemv_launches,
