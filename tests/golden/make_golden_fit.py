@@ -1,6 +1,6 @@
 """Generates tests/golden/fit_cases.npz: inputs and results of the REFERENCE's alternating fit.
 
-    python tests/golden/make_golden_fit.py            (needs /root/reference; CPU only)
+    python tests/golden/make_golden_fit.py <path of the ELUTQ checkout>       (CPU only)
 
 Runs the reference's own pseudo_quantize_tensor(..., use_alternating_optimization=True)
 (GPTQ/quant.py:185-213 -> find_optimal_params_alternating :118-153 -> quantize_with_scales
@@ -15,13 +15,12 @@ import sys
 import numpy as np
 import torch
 
-REF = "/root/reference/GPTQ"
 HERE = os.path.dirname(os.path.abspath(__file__))
 CASES = [(2, 64), (2, 128), (3, 64), (3, 128), (4, 128)]
 
 
-def main():
-    sys.path.insert(0, REF)
+def main(reference_root):
+    sys.path.insert(0, os.path.join(reference_root, "GPTQ"))
     import quant
     out = {}
     for ci, (q, g) in enumerate(CASES):
@@ -46,4 +45,6 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])

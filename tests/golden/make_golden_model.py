@@ -1,9 +1,9 @@
 """Generates tests/golden/model_tiny_llama.npz: a whole-model export directory written by the
 REFERENCE's own quantizer driver, plus the logits of the model it evaluates.
 
-    python tests/golden/make_golden_model.py            (needs /root/reference and transformers; CPU only)
+    python tests/golden/make_golden_model.py <path of the ELUTQ checkout>      (needs transformers; CPU only)
 
-What runs is the reference's code, unmodified, imported from /root/reference/GPTQ:
+What runs is the reference's code, unmodified, imported from the checkout's GPTQ directory:
   export_llama_weights      GPTQ/llama.py:286-343   embeddings, norms (fp16 .bin files)
   llama_sequential          GPTQ/llama.py:31-180    per layer: HLQ.add_batch (Hessian) and
                                                     HLQ.fasterquant(output_dir=...) for every linear,
@@ -31,13 +31,12 @@ import types
 
 import numpy as np
 
-REF = "/root/reference/GPTQ"
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def main():
+def main(reference_root):
     sys.modules.setdefault("termcolor", types.SimpleNamespace(colored=lambda s, *a, **k: s))
-    sys.path.insert(0, REF)
+    sys.path.insert(0, os.path.join(reference_root, "GPTQ"))
     import torch
     torch.cuda.synchronize = lambda *a, **k: None
     import llama as ref_llama
@@ -83,4 +82,6 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])
