@@ -123,3 +123,29 @@ def test_chain_request_falls_back_where_the_kernel_does_not_apply(tmp_path):
     ref = d["logits"][0].astype(np.float64)
     got = dec.last_logits.float().cpu().numpy()[0].astype(np.float64)
     assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2
+
+
+@pytest.mark.timeout(180)
+def test_chain_against_the_decoder_oracle(tmp_path):
+    """A small exported model (heads of 128 channels) through the decode chain, token by token, against
+    the CPU decoder oracle (the reference model's op order over the float64 oracles): logits of six
+    consecutive positions to 1e-2 normwise, the final hidden state to 2e-2 in relative L2."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from test_model_io import tiny_model
+    from elutq_b200.decoder import TPDecoder
+    from oracle.decoder_oracle import OracleDecoder
+    m = tiny_model(layers=2, hidden=256, ffn=512, heads=4, kv=2, dhead=128, vocab=320, quant_head=True, seed=11)
+    dec = TPDecoder.from_export(m, n_heads=4, n_kv=2, device=torch.device("cuda", 0), ctx=64, rope_theta=1e4, chain=True)
+    assert dec.use_chain
+    ora = OracleDecoder(m, 4, 2, 1e4, 1e-5, ctx=64)
+    tokens = [5, 17, 300, 2, 41, 9]
+    for pos, tok in enumerate(tokens):
+        dec.position.fill_(pos)
+        dec.step_eager(tok)
+        torch.cuda.synchronize()
+        assert dec.chain.status() == 0 and dec.attn.status() == 0
+        want, hidden = ora.step(tok, pos)
+        got = dec.last_logits.float().cpu().numpy()[0].astype(np.float64)
+        assert np.abs(got - want).max() / np.abs(want).max() <= 1e-2, pos
