@@ -312,6 +312,40 @@ def test_group_launch_matches_oracle_and_single_launches(L):
             grp.forward(m + 1)                  # more rows than the group's scratch holds
 
 
+def test_large_group_matches_single_launches(L):
+    """A group of 78 linears (every CTA walks a dozen segments of several members): the same numbers as
+    one launch per member (same tables, same sums; fp32 atomics in another order), three times in a row."""
+    lm = linear_mod()
+    gen = torch.Generator(device="cuda")
+    shapes = [(4096, 4096), (2048, 8192), (1024, 4096)] * 26
+    ws, xs, ys, refs = [], [], [], []
+    for i, (n, k) in enumerate(shapes):
+        gen.manual_seed(1000 + i)
+        wq = torch.randint(0, 256, (2, n, k // 8), dtype=torch.uint8, device="cuda", generator=gen)
+        sc = (torch.randn((2, n, k // 128), device="cuda", generator=gen) * 0.02).abs().half()
+        zz = (torch.randn((n, k // 128), device="cuda", generator=gen) * 0.01).half()
+        ws.append(lm.HLQWeight.from_export(F.ExportedLinear(wq, sc, zz, None, 128), device=0))
+        xs.append(torch.randn((1, k), device="cuda", generator=gen).half())
+        ys.append(torch.zeros((1, n), dtype=torch.float32, device="cuda"))
+    wsp = lm.Workspace(lm.workspace_bytes(1, 8192, 4096, 2, 128), torch.device("cuda", 0))
+    for w, x in zip(ws, xs):
+        refs.append(lm.linear_forward(x, w, wsp, out_dtype=torch.float32).clone())
+    group = lm.HLQGroup(ws, max_m=1)
+    group.bind(xs, ys)
+    for _ in range(3):
+        for y in ys:
+            y.zero_()
+        group.forward(1)
+        torch.cuda.synchronize()
+        assert group.kernel_status() == 0
+        for y, ref in zip(ys, refs):
+            assert O.normwise_error(y.cpu().numpy(), ref.cpu().numpy()) <= 1e-6
+    # one member against the oracle
+    e = ws[1].to_export()
+    ref = O.hlq_linear(xs[1].cpu().numpy().astype(np.float32), e.w_quant, e.w_scale, e.w_zero, 128, dtype=np.float32)
+    assert O.normwise_error(ys[1].cpu().numpy(), ref) <= 2e-5
+
+
 def test_group_rejects_mixed_members(L):
     lm = linear_mod()
     a = make(O.synth_linear(64, 512, 2, 128, seed=1), 128)[1]
