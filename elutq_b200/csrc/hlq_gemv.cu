@@ -733,6 +733,7 @@ Workspace carve_workspace(void *base, int m, const StreamDims &d) {
 
 static DeviceInfo g_dev[64];
 std::mutex g_first_use;
+std::atomic<int> g_batch_kernel{0};
 
 int device_info(int device, DeviceInfo **out) {
     if (device < 0 || device >= 64) return HLQ_ERR_INVALID_ARGUMENT;
@@ -801,7 +802,11 @@ static int launch_lut8_any(int q, int gpw, const GemvArgs &a_in, dim3 grid, cuda
     GemvArgs a = a_in;
     a.row_base = 0;
     if (a.one_row_passes) return launch_lut8_rows<1, true>(q, gpw, a, grid, stream);
-    if (!lut_only && !a.tp && !a.y_is_f32 && batch_mma_supported(q, m)) return launch_batch_mma(q, gpw, a, (int)grid.x, m, stream);
+    if (!lut_only && !a.tp && !a.y_is_f32 && batch_mma_supported(q, m)) {
+        // by measurement: the mma.sync kernel is the faster of the two at every m <= 16 (hlq_batch_umma.cu)
+        if (g_batch_kernel.load(std::memory_order_relaxed) == 2) return launch_batch_umma(q, gpw, a, (int)grid.x, m, stream);
+        return launch_batch_mma(q, gpw, a, (int)grid.x, m, stream);
+    }
     if (m < 2 || a.tp || a.y_is_f32) return launch_lut8_rows<1, false>(q, gpw, a, grid, stream);
     int rc = launch_lut8_rows<2, false>(q, gpw, a, dim3(grid.x, m / 2), stream);
     if (rc || !(m & 1)) return rc;
@@ -983,6 +988,12 @@ extern "C" int hlq_linear_forward_static(int m, int k, int n, const void *d_x, i
     HLQ_CUDA(cudaGetDevice(&cur));
     if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;   // the weight's device must be current
     return hlq::launch_lut8_gemv_static(w, m, d_x, x_dtype, d_y, y_dtype, (cudaStream_t)stream);
+}
+
+extern "C" int hlq_select_batch_kernel(int which) {
+    if (which < 0 || which > 2) return HLQ_ERR_INVALID_ARGUMENT;
+    hlq::g_batch_kernel.store(which, std::memory_order_relaxed);
+    return HLQ_OK;
 }
 
 extern "C" int hlq_static_scratch_status(int device, void *stream, int *kernel_status) {

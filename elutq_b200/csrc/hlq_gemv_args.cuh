@@ -196,6 +196,10 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
 // The small-batch kernel (hlq_batch.cu): whether it takes (q, m), and its launch over the jobs of `a`.
 bool batch_mma_supported(int q, int m);
 int launch_batch_mma(int q, int gpw, const GemvArgs &a, int ctas, int m, cudaStream_t stream);
+// The same launch on the tcgen05 tensor cores (hlq_batch_umma.cu).
+int launch_batch_umma(int q, int gpw, const GemvArgs &a, int ctas, int m, cudaStream_t stream);
+// Which of the two serves small batches: 0 = the default, 1 = mma.sync, 2 = tcgen05 (hlq_select_batch_kernel).
+extern std::atomic<int> g_batch_kernel;
 // The code words of a weight in the streaming layout (hlq_weight_build_batch_codes): device buffer of
 // slices * duos * kCodeDuoBytes bytes from its planes.
 int launch_build_codes(int q, const uint8_t *planes, uint8_t *codes, int slices, int duos, cudaStream_t stream);

@@ -234,6 +234,12 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
                             void *d_y, int y_dtype, void *d_workspace, size_t workspace_bytes,
                             const hlq_weight *w, void *stream);
 
+/* Which kernel serves 3..16 rows of activations (for tests and measurements, process-wide):
+ * 0 = the default (1), 1 = register dequantization + mma.sync, 2 = register dequantization +
+ * tcgen05.mma with the weight operand in shared memory and the accumulators in tensor memory
+ * (correct, at present the slower of the two).  Same results up to fp32 summation order. */
+int hlq_select_batch_kernel(int which);
+
 /* The same product as hlq_linear_forward for a weight in the streaming layout, for callers
  * that must not allocate device memory around the call and therefore have no workspace to
  * pass: a serving process whose own memory manager took all of HBM at start-up, or a

@@ -139,3 +139,25 @@ def test_code_words_in_a_group_at_llama_shapes(L):
     for d, y in zip(ds, ys):
         ref = O.hlq_linear(d["x"].astype(np.float32), d["w_quant"], d["w_scale"], d["w_zero"], 128, dtype=np.float32)
         assert O.normwise_error(y.float().cpu().numpy(), ref) <= TOL_F16
+
+
+@pytest.mark.parametrize("q,g", [(2, 128), (3, 128), (3, 64), (2, 32)])
+def test_tcgen05_variant_gives_the_same_numbers(L, q, g):
+    """The selectable tcgen05 kernel (weights dequantized into a shared-memory operand, accumulators
+    in tensor memory) against the oracle and against the default kernel, with and without code words."""
+    d = O.synth_linear(328, 1664, q, g, m=16, seed=11 * q + g, bias=True, signed_alpha=True)
+    mod = make(d, g, max_batch=16)
+    ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
+    x = torch.from_numpy(d["x"]).cuda()
+    base = {m: forward(mod, x[:m]) for m in (3, 8, 13, 16)}
+    try:
+        _lib.check(L.hlq_select_batch_kernel(2), "hlq_select_batch_kernel")
+        for coded in (False, True):
+            if coded:
+                mod.weight.build_batch_codes()
+            for m in (3, 8, 13, 16):
+                y = forward(mod, x[:m])
+                assert O.normwise_error(y, ref[:m]) <= TOL_F16, (m, coded)
+                assert O.normwise_error(y, base[m]) <= 2e-3, (m, coded)
+    finally:
+        L.hlq_select_batch_kernel(0)
