@@ -120,6 +120,10 @@ __device__ __forceinline__ void umma_commit(uint32_t mbar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar)
                  : "memory");
 }
+// asks the L2 for `bytes` (a multiple of 16, from a 16-byte boundary) of global memory; nothing waits for it
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bu_cp_async_16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -200,6 +204,19 @@ __global__ void __launch_bounds__(kBuThreads, 1) batch_umma_kernel(const __grid_
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kBarDesc + slot));
             if (!sg.live) return;
+            {
+                // The segment's weights into the L2, one segment ahead of the dequantizers: a warp
+                // keeps only one oct of loads in flight, which covers the L2's latency, not HBM's.
+                constexpr uint32_t kDuoBytes = CODES ? kCodeDuoBytes : 2 * Q * kCellBytes;
+                constexpr uint32_t kMetaBytes = (Q + 1) * 32 * 2 * GPW * 2;
+                const int nd = sg.duo_b - sg.duo_a;
+                const uint8_t *pl = CODES ? sg.codes : sg.planes;
+                for (int d0 = 8 * lane; d0 < nd; d0 += 8 * 32) {
+                    const uint32_t cnt = (uint32_t)min(8, nd - d0);
+                    bulk_prefetch_l2(pl + (long long)d0 * kDuoBytes, cnt * kDuoBytes);
+                    bulk_prefetch_l2((const uint8_t *)sg.meta + (long long)d0 * kMetaBytes, cnt * kMetaBytes);
+                }
+            }
             if (!waited) {
                 pdl_wait();
                 waited = true;
