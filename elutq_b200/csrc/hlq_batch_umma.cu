@@ -33,11 +33,13 @@
 // Status: bit-for-bit the same tables and selectors as batch_mma_kernel and the same results, but
 // at present SLOWER (8B projection set at w3g128: 1.65 / 1.95 ms for 4 / 16 rows against 1.02 /
 // 1.34), so the dispatcher keeps batch_mma_kernel and this kernel runs only when selected
-// (hlq_select_batch_kernel).  Builds without the dequantization take 0.28 ms per 8 layers, builds
-// without the tcgen05.mma 0.40, the whole 0.45: the lock-step of 16 warps per half tile (every half
-// waits for its slowest warp, then for the single issuing thread's 16 instructions and their
-// commit) costs more than the 8 cycles per mma.sync it saves.  What it would take: K steps handed
-// over one by one instead of four at a time, and more than one tile of loads in flight per warp.
+// (hlq_select_batch_kernel).  On 8 layers with 4 rows: the whole 0.43 ms; without the dequantization
+// 0.28, without the tcgen05.mma 0.40, without the proxy fences 0.43, and without the stores of the
+// dequantized weights 0.28 - the integer work hides completely, what costs is shared memory: an
+// fp16 weight is written once (2 bytes) and read once by the tensor cores (2 bytes), 256 KB per
+// tile of 128 rows against 128 bytes per clock.  The way out is a weight operand that never
+// passes shared memory (tcgen05.st into tensor memory, which wants a lane to own a whole row,
+// i.e. another weight layout); not built.
 //
 // Every wait is an mbarrier wait with a poll limit; the first one that runs out sets the CTA's
 // failure flag, after which all waits give up at once and the roles run out of work.
