@@ -104,6 +104,11 @@ static void free_buffers(hlq_weight *w) {
     if (w->d_codes) cudaFree(w->d_codes);
     w->d_codes = nullptr;
     w->codes_bytes = 0;
+    if (w->d_rcodes) cudaFree(w->d_rcodes);
+    if (w->d_rmeta) cudaFree(w->d_rmeta);
+    w->d_rcodes = nullptr;
+    w->d_rmeta = nullptr;
+    w->rcodes_bytes = 0;
     free_sparse(w);
     w->d_planes = nullptr;
     w->d_meta = nullptr;
@@ -301,7 +306,7 @@ int hlq_weight_get_info(const hlq_weight *w, hlq_weight_info *info) {
     info->shard_mode = w->shard_mode;
     info->full_in_channel = w->k_full;
     info->full_out_channel = w->n_full;
-    info->device_bytes = w->planes_bytes + w->meta_bytes + w->codes_bytes + (w->d_bias ? (int64_t)w->n * 2 : 0);
+    info->device_bytes = w->planes_bytes + w->meta_bytes + w->codes_bytes + w->rcodes_bytes + (w->d_bias ? (int64_t)w->n * 2 : 0);
     info->algorithmic_bytes = (int64_t)w->q * w->n * (w->k / 8) + 2 * (int64_t)(w->q + 1) * w->n * (w->k / w->g);
     return HLQ_OK;
 }
@@ -335,6 +340,23 @@ int hlq_weight_build_batch_codes(hlq_weight *w, void *stream) {
     }
     w->d_codes = p;
     w->codes_bytes = bytes;
+    // where the shape allows, also the codes with a row per lane (hlq_batch_tmem.cu)
+    if (w->g == 128 && d.np % 128 == 0) {
+        const int64_t tiles = (int64_t)d.slices * (d.np / 128);
+        uint8_t *rc = nullptr;
+        uint16_t *rm = nullptr;
+        if (cudaMalloc((void **)&rc, (size_t)(tiles * hlq::kRowCodeTileBytes)) == cudaSuccess &&
+            cudaMalloc((void **)&rm, (size_t)(tiles * hlq::kRowMetaTileBytes)) == cudaSuccess &&
+            hlq::launch_build_row_codes(w->q, w->d_planes, w->d_meta, rc, rm, d, (cudaStream_t)stream) == HLQ_OK) {
+            w->d_rcodes = rc;
+            w->d_rmeta = rm;
+            w->rcodes_bytes = tiles * (hlq::kRowCodeTileBytes + hlq::kRowMetaTileBytes);
+        } else {
+            if (rc) cudaFree(rc);
+            if (rm) cudaFree(rm);
+            return hlq::note_cuda(cudaGetLastError()) ? HLQ_ERR_CUDA : HLQ_ERR_CUDA;
+        }
+    }
     return HLQ_OK;
 }
 

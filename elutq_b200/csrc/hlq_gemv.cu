@@ -804,7 +804,9 @@ static int launch_lut8_any(int q, int gpw, const GemvArgs &a_in, dim3 grid, cuda
     if (a.one_row_passes) return launch_lut8_rows<1, true>(q, gpw, a, grid, stream);
     if (!lut_only && !a.tp && !a.y_is_f32 && batch_mma_supported(q, m)) {
         // by measurement: the mma.sync kernel is the faster of the two at every m <= 16 (hlq_batch_umma.cu)
-        if (g_batch_kernel.load(std::memory_order_relaxed) == 2) return launch_batch_umma(q, gpw, a, (int)grid.x, m, stream);
+        const int which = g_batch_kernel.load(std::memory_order_relaxed);
+        if (which == 3 && a.use_rcodes && gpw == 1) return launch_batch_tmem(q, gpw, a, (int)grid.x, m, stream);
+        if (which == 2) return launch_batch_umma(q, gpw, a, (int)grid.x, m, stream);
         return launch_batch_mma(q, gpw, a, (int)grid.x, m, stream);
     }
     if (m < 2 || a.tp || a.y_is_f32) return launch_lut8_rows<1, false>(q, gpw, a, grid, stream);
@@ -819,6 +821,8 @@ static void fill_job(Job &j, const hlq_weight *w, const StreamDims &d, const voi
     j.planes = w->d_planes;
     j.meta = w->d_meta;
     j.codes = w->d_codes;
+    j.rcodes = w->d_rcodes;
+    j.rmeta = w->d_rmeta;
     j.bias = w->d_bias;
     j.acc = partial;
     j.counters = counters;
@@ -885,6 +889,7 @@ int launch_lut8_gemv(const hlq_weight *w, int m, const void *x, int x_dtype, voi
         a.spin_limit = kDefaultSpinLimit;
         a.y_is_f32 = y_dtype == HLQ_F32;
         a.use_codes = w->d_codes != nullptr;
+        a.use_rcodes = w->d_rcodes != nullptr;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         rc = apply_input_op(a.single, op, x_dtype, m0);
@@ -965,6 +970,7 @@ int launch_lut8_gemv_static(const hlq_weight *w, int m, const void *x, int x_dty
         a.spin_limit = kDefaultSpinLimit;
         a.y_is_f32 = y_dtype == HLQ_F32;
         a.use_codes = w->d_codes != nullptr;
+        a.use_rcodes = w->d_rcodes != nullptr;
         fill_job(a.single, w, d, (const char *)x + (size_t)m0 * w->k * xsz, x_dtype,
                  (char *)y + (size_t)m0 * w->n * ysz, y_dtype, ws.partial, ws.counters, 0);
         int ctas = di->sms;
@@ -991,7 +997,7 @@ extern "C" int hlq_linear_forward_static(int m, int k, int n, const void *d_x, i
 }
 
 extern "C" int hlq_select_batch_kernel(int which) {
-    if (which < 0 || which > 2) return HLQ_ERR_INVALID_ARGUMENT;
+    if (which < 0 || which > 3) return HLQ_ERR_INVALID_ARGUMENT;
     hlq::g_batch_kernel.store(which, std::memory_order_relaxed);
     return HLQ_OK;
 }
@@ -1198,6 +1204,7 @@ struct hlq_group {
     int seg_cost = 0;
     bool one_row_passes = false;  // a member has an input transform
     bool use_codes = false;       // every member had code words when the group was made
+    bool use_rcodes = false;      // ... and row codes
     std::vector<const hlq_weight *> weights;
     std::vector<hlq::Job> jobs_host;
     hlq::Job *d_jobs = nullptr;
@@ -1267,8 +1274,11 @@ int hlq_group_create(hlq_group **out, int count, const hlq_weight *const *weight
         }
         g->total_units = ub;
         g->total_units_chunked = ubc;
-        g->use_codes = true;
-        for (int i = 0; i < count; ++i) g->use_codes = g->use_codes && weights[i]->d_codes != nullptr;
+        g->use_codes = g->use_rcodes = true;
+        for (int i = 0; i < count; ++i) {
+            g->use_codes = g->use_codes && weights[i]->d_codes != nullptr;
+            g->use_rcodes = g->use_rcodes && weights[i]->d_rcodes != nullptr;
+        }
     }
     if (prev >= 0) cudaSetDevice(prev);
     if (rc) {
@@ -1329,6 +1339,7 @@ int hlq_group_forward(hlq_group *g, int m, void *stream) {
     a.total_units = g->total_units;
     a.total_units_chunked = g->total_units_chunked;
     a.use_codes = g->use_codes;
+    a.use_rcodes = g->use_rcodes;
     a.seg_cost = g->seg_cost;
     a.status = (int *)g->d_scratch;
     a.dyn_smem = kLut8DynSmem;

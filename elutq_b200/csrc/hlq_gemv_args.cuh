@@ -14,6 +14,8 @@ struct Job {
     const uint8_t *planes;
     const uint16_t *meta;
     const uint8_t *codes; // optional second copy of the planes as 4-bit code words (hlq_batch.cu), or nullptr
+    const uint8_t *rcodes;   // optional: the codes once more with a row per lane, and the scales and zeros
+    const uint16_t *rmeta;   // in that order (hlq_batch_tmem.cu), or nullptr
     const uint16_t *bias;
     float *acc;           // [m][np] fp32 accumulators, zero between launches
     unsigned *counters;   // [m][blocks]
@@ -49,6 +51,8 @@ struct GemvArgs {
     int spin_limit;       // polls after which a bounded wait gives up
     int batch_rows;       // small-batch kernel: rows of x of the launch (all served by one pass)
     int use_codes;        // small-batch kernel: every job of the launch has code words
+    int use_rcodes;       // ... and row codes (then every job's duos are a multiple of 8)
+    int unit_align;       // 0 or 1: a CTA's share starts anywhere; 8: on a multiple of 8 units
     int chunk_duos;       // 0: a job's units run slice by slice over all its duos; else chunk by chunk of
                           // this many duos, all slices of a chunk before the next chunk (then total_units
                           // and the jobs' unit_begin_chunked count seg_cost per (slice, chunk))
@@ -59,6 +63,8 @@ struct GemvArgs {
 struct Seg {
     const uint8_t *planes;  // first cell of the segment
     const uint8_t *codes;   // first code words of the segment (jobs that have them), else nullptr
+    const uint8_t *rcodes;  // row codes and their scales of the segment's first tile of 128 rows, else nullptr
+    const uint16_t *rmeta;
     const uint16_t *meta;   // first meta entry of the segment
     const uint16_t *bias;
     float *acc;             // accumulator row base of mrow
@@ -89,7 +95,9 @@ __host__ __device__ static inline long long launch_units(int slices, int duos, i
 // job's last slice.  Its segments cost little beside their duos.
 constexpr int kChunkDuos = 128;
 constexpr int kCodeDuoBytes = 4096;     // code words of one duo: 16 rows x 512 channels x 4 bits
-constexpr int kChunkSegCost = 4;
+constexpr int kRowCodeTileBytes = 32768; // row codes of one tile: 128 rows x 512 channels x 4 bits, [quarter][chunk][row][16]
+constexpr int kRowMetaTileBytes = 4096;  // their scales and zeros: [quarter][row][4] fp16
+constexpr int kChunkSegCost = 8;     // a multiple of 8, so that cuts on multiples of 8 units fall on tiles of 8 duos
 __host__ __device__ static inline long long launch_units_chunked(int slices, int duos, int chunk, int seg_cost) {
     const int chunks = (duos + chunk - 1) / chunk;
     return (long long)slices * duos + (long long)slices * chunks * seg_cost;
@@ -113,8 +121,9 @@ __device__ __forceinline__ long long walker_job_units(const GemvArgs &a, const J
 
 __device__ __forceinline__ void walker_init(Walker &w, const GemvArgs &a, int mrow) {
     w.a = &a;
-    w.u = a.total_units * blockIdx.x / gridDim.x;
-    w.u_end = a.total_units * (blockIdx.x + 1) / gridDim.x;
+    const long long al = a.unit_align > 1 ? a.unit_align : 1;
+    w.u = a.total_units / al * blockIdx.x / gridDim.x * al;
+    w.u_end = blockIdx.x + 1 == gridDim.x ? a.total_units : a.total_units / al * (blockIdx.x + 1) / gridDim.x * al;
     w.mrow = mrow;
     w.jidx = 0;
     if (a.njobs == 0) {
@@ -175,6 +184,13 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
     const long long cell = (long long)s * jb.duos + chunk_first + da;           // in duos
     sg.planes = jb.planes + cell * (2 * Q * kCellBytes);
     sg.codes = jb.codes ? jb.codes + cell * kCodeDuoBytes : nullptr;
+    sg.rcodes = nullptr;
+    sg.rmeta = nullptr;
+    if (jb.rcodes) {
+        const long long tile = (long long)s * (jb.duos / 8) + (chunk_first + da) / 8;     // tiles of 8 duos
+        sg.rcodes = jb.rcodes + tile * kRowCodeTileBytes;
+        sg.rmeta = jb.rmeta + tile * (kRowMetaTileBytes / 2);
+    }
     sg.meta = jb.meta + cell * ((Q + 1) * 32 * 2 * GPW);
     sg.bias = jb.bias;
     sg.acc = jb.acc + (long long)w.mrow * jb.np;
@@ -196,6 +212,11 @@ __device__ __forceinline__ const uint16_t *walker_next(Walker &w, Seg &sg, int &
 // The small-batch kernel (hlq_batch.cu): whether it takes (q, m), and its launch over the jobs of `a`.
 bool batch_mma_supported(int q, int m);
 int launch_batch_mma(int q, int gpw, const GemvArgs &a, int ctas, int m, cudaStream_t stream);
+// The same launch with the weight operand in tensor memory (hlq_batch_tmem.cu; needs a.use_rcodes).
+int launch_batch_tmem(int q, int gpw, const GemvArgs &a, int ctas, int m, cudaStream_t stream);
+// Row codes of a weight (g = 128, 2 or 3 bits, rows a multiple of 128) from its planes and meta.
+int launch_build_row_codes(int q, const uint8_t *planes, const uint16_t *meta, uint8_t *rcodes, uint16_t *rmeta,
+                           const StreamDims &d, cudaStream_t stream);
 // The same launch on the tcgen05 tensor cores (hlq_batch_umma.cu).
 int launch_batch_umma(int q, int gpw, const GemvArgs &a, int ctas, int m, cudaStream_t stream);
 // Which of the two serves small batches: 0 = the default, 1 = mma.sync, 2 = tcgen05 (hlq_select_batch_kernel).

@@ -24,6 +24,11 @@ struct hlq_weight {
     // which the small-batch kernel reads instead of the planes (hlq_weight_build_batch_codes)
     uint8_t *d_codes = nullptr;
     int64_t codes_bytes = 0;
+    // ... and, where the shape allows (g = 128, rows a multiple of 128), the codes with a row per lane
+    // plus the scales and zeros in that order, for the kernel that keeps its weight operand in tensor memory
+    uint8_t *d_rcodes = nullptr;
+    uint16_t *d_rmeta = nullptr;
+    int64_t rcodes_bytes = 0;
     // HLQ_LAYOUT_EXPORT only: 256 zeroed bytes whose first word is the generic kernel's status
     // word when a forward call brings no workspace (allocated with the handle, never in a
     // launch path).

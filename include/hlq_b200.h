@@ -193,8 +193,10 @@ int hlq_weight_get_sparse(const hlq_weight *w, uint32_t *h_mask, uint8_t *h_bloc
  * code word per weight (the planes' bits of a weight side by side; n_pad * k_pad / 2 bytes of device
  * memory, counted in hlq_weight_info.device_bytes).  Calls with 3..16 rows of activations then read
  * the code words instead of the planes and skip the bit gathering that binds them (their results
- * are the same numbers).  Build it before the weight is put into a group; it is freed with the
- * handle and never exported.  No counterpart in the reference. */
+ * are the same numbers).  For g = 128 and rows a multiple of 128 the call also stores the codes a
+ * third time with one row per lane ("row codes", as many bytes again plus 8 bytes per group), which
+ * only the kernel that hlq_select_batch_kernel(3) selects reads.  Build it before the weight is put
+ * into a group; it is freed with the handle and never exported.  No counterpart in the reference. */
 int hlq_weight_build_batch_codes(hlq_weight *w, void *stream);
 
 /* ---- forward ------------------------------------------------------------------------ */
@@ -237,7 +239,10 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
 /* Which kernel serves 3..16 rows of activations (for tests and measurements, process-wide):
  * 0 = the default (1), 1 = register dequantization + mma.sync, 2 = register dequantization +
  * tcgen05.mma with the weight operand in shared memory and the accumulators in tensor memory
- * (correct, at present the slower of the two).  Same results up to fp32 summation order. */
+ * (correct, the slowest of the three), 3 = tcgen05.mma with the weight operand in tensor memory
+ * (needs the row codes that hlq_weight_build_batch_codes makes for 2- and 3-bit weights with
+ * g = 128 and rows a multiple of 128; other weights fall back to 1; as fast as 1 at 16 rows,
+ * slower below).  Same results up to fp32 summation order. */
 int hlq_select_batch_kernel(int which);
 
 /* The same product as hlq_linear_forward for a weight in the streaming layout, for callers

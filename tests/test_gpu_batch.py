@@ -161,3 +161,31 @@ def test_tcgen05_variant_gives_the_same_numbers(L, q, g):
                 assert O.normwise_error(y, base[m]) <= 2e-3, (m, coded)
     finally:
         L.hlq_select_batch_kernel(0)
+
+
+@pytest.mark.parametrize("q", [2, 3])
+def test_tensor_memory_operand_variant_gives_the_same_numbers(L, q):
+    """The selectable kernel whose weight operand lives in tensor memory (row codes, g = 128, rows a
+    multiple of 128): against the oracle and the default kernel, one launch and a group of weights,
+    with activations that change between calls so that a launch that wrote nothing cannot pass."""
+    d = O.synth_linear(384, 1664, q, 128, m=16, seed=23 * q, bias=True, signed_alpha=True)
+    mod = make(d, 128, max_batch=16)
+    mod.weight.build_batch_codes()
+    ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], 128, d["bias"])
+    half = (d["x"] * np.float16(0.5)).astype(np.float16)
+    ref_half = O.hlq_linear(half, d["w_quant"], d["w_scale"], d["w_zero"], 128, d["bias"])
+    x, xh = torch.from_numpy(d["x"]).cuda(), torch.from_numpy(half).cuda()
+    for m in (3, 8, 13, 16):
+        assert O.normwise_error(forward(mod, x[:m]), ref[:m]) <= TOL_F16, m
+    try:
+        _lib.check(L.hlq_select_batch_kernel(3), "hlq_select_batch_kernel")
+        for m in (3, 8, 13, 16):
+            assert O.normwise_error(forward(mod, xh[:m]), ref_half[:m]) <= TOL_F16, m
+        # a weight without row codes (rows not a multiple of 128) is served by the default kernel
+        d2 = O.synth_linear(328, 1152, q, 128, m=8, seed=5, bias=False)
+        mod2 = make(d2, 128, max_batch=16)
+        mod2.weight.build_batch_codes()
+        ref2 = O.hlq_linear(d2["x"], d2["w_quant"], d2["w_scale"], d2["w_zero"], 128, None)
+        assert O.normwise_error(forward(mod2, torch.from_numpy(d2["x"]).cuda()), ref2) <= TOL_F16
+    finally:
+        L.hlq_select_batch_kernel(0)
