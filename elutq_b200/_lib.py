@@ -65,6 +65,7 @@ SIGNATURES = {
     "hlq_weight_sparse_pairs": (c_int, [c_void_p, POINTER(c_int)]),
     "hlq_weight_build_batch_codes": (c_int, [c_void_p, c_void_p]),
     "hlq_select_batch_kernel": (c_int, [c_int]),
+    "hlq_select_prefill_kernel": (c_int, [c_int]),
     "hlq_weight_get_sparse": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "hlq_workspace_bytes": (c_size_t, [c_int] * 5),
     "hlq_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),

@@ -14,8 +14,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libhlq_b200.so")
-SOURCES = ["hlq_host.cpp", "hlq_layout.cu", "hlq_gemv.cu", "hlq_batch.cu", "hlq_batch_umma.cu", "hlq_batch_tmem.cu", "hlq_gemm.cu", "hlq_glue.cu", "hlq_chain.cu", "hlq_sparse.cu", "hlq_fit.cu", "hlq_api.cu"]
-HEADERS = ["hlq_layout.h", "hlq_internal.h", "hlq_gemv_dev.cuh", "hlq_gemv_args.cuh", "hlq_batch_dev.cuh", "hlq_attn_dev.cuh", os.path.join("..", "..", "include", "hlq_b200.h")]
+SOURCES = ["hlq_host.cpp", "hlq_layout.cu", "hlq_gemv.cu", "hlq_batch.cu", "hlq_batch_umma.cu", "hlq_batch_tmem.cu", "hlq_gemm.cu", "hlq_gemm_pair.cu", "hlq_glue.cu", "hlq_chain.cu", "hlq_sparse.cu", "hlq_fit.cu", "hlq_api.cu"]
+HEADERS = ["hlq_layout.h", "hlq_internal.h", "hlq_gemv_dev.cuh", "hlq_gemv_args.cuh", "hlq_batch_dev.cuh", "hlq_gemm_dev.cuh", "hlq_attn_dev.cuh", os.path.join("..", "..", "include", "hlq_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -25,22 +25,14 @@
 // All mbarrier waits are bounded; on expiry the CTA sets the status word and carries on to
 // its exit so that tensor memory is always released.
 #include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstdlib>
 
-#include "hlq_internal.h"
+#include "hlq_gemm_dev.cuh"
 
 namespace hlq {
 namespace gemm {
-
-constexpr int kTileK = 64;        // channels per K step: 128 bytes of 16-bit operands
-constexpr int kMaxTileM = 256;    // tokens per CTA at most (UMMA N)
-constexpr uint32_t kXBytes = kMaxTileM * kTileK * 2;   // 32 KB reserved per stage
-constexpr uint32_t kLutBytes = 256 * 16;
-constexpr uint32_t kBarBytes = 256;
-constexpr int kSpinLimit = 1 << 24;
 
 template <int ROWS>
 struct Cfg {
@@ -53,118 +45,6 @@ struct Cfg {
     static constexpr uint32_t kDynSmem = 1024 + kStages * kStageBytes + kLutBytes + kBarBytes;
     static constexpr uint32_t kTmemCols = 256 * kAcc;
 };
-
-struct GemmArgs {
-    const uint8_t *planes;
-    const uint16_t *meta;
-    const uint16_t *bias;
-    void *y;
-    int *status;
-    int m, n, k, np, kp, octs, duos, gpw, gshift;
-    int tile_m;          // tokens per CTA: multiple of 32, <= 256
-    int y_dtype;
-};
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
-    for (int i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(mbar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t mbar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(mbar) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row atoms of 1024 bytes.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;              // stride between 8-row atoms
-    d |= (uint64_t)1 << 46;                        // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
-    return d;
-}
-// kind::f16 instruction descriptor: fp32 accumulator, A and B fp16, both K-major, M = 128,
-// N = tokens per tile.
-__device__ __forceinline__ uint32_t umma_idesc(int tile_m) {
-    return (1u << 4) | ((uint32_t)(tile_m >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t mbar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar)
-                 : "memory");
-}
-
-// What a dequantizer thread fetches for one K step: the 4 bytes per plane that hold its 32
-// channels of its row, and the fp16 scales / zero of the group they fall into.
-template <int Q>
-struct Raw {
-    uint32_t w[Q];
-    uint16_t al[Q];
-    uint16_t z;
-};
-
-// hh = which 32-channel half of the 64-channel K step this thread owns
-template <int Q>
-__device__ __forceinline__ void load_raw(Raw<Q> &rw, const GemmArgs &a, int kt, int oct, int r, int hh,
-                                         bool row_ok) {
-    const int k0 = kt * kTileK;
-    const int sl = k0 >> 9, j = (k0 >> 7) & 3, h = (k0 >> 6) & 1;
-    const int ln = r * 4 + j;
-    const int half = h ^ (r >> 2);            // which 8 bytes of the lane word hold the 64 channels
-    const int word = hh ^ ((r & 3) >> 1);     // and which 4 of those hold this thread's two byte pairs
-#pragma unroll
-    for (int p = 0; p < Q; ++p) {
-        rw.w[p] = 0u;
-        if (row_ok)
-            rw.w[p] = __ldg((const uint32_t *)(a.planes + (((int64_t)sl * a.octs + oct) * Q + p) * kCellBytes +
-                                               ln * 16 + 8 * half + 4 * word));
-    }
-    // source sub-group inside the lane's 128 channels: g = 128 -> 0, g = 64 -> h, g = 32 -> 2h + hh
-    const int su = a.gpw == 1 ? 0 : (a.gpw == 2 ? h : 2 * h + hh);
-    const int u = su ^ (r >> a.gshift);
-    const int64_t mbase = ((((int64_t)sl * a.duos + (oct >> 1)) * (Q + 1)) * 32 + ln) * 2 * a.gpw +
-                          (oct & 1) * a.gpw + u;
-    const int64_t pstride = (int64_t)32 * 2 * a.gpw;
-#pragma unroll
-    for (int p = 0; p < Q; ++p) rw.al[p] = row_ok ? __ldg(a.meta + mbase + p * pstride) : (uint16_t)0;
-    rw.z = row_ok ? __ldg(a.meta + mbase + Q * pstride) : (uint16_t)0;
-}
 
 template <int ROWS, int Q>
 __global__ void __launch_bounds__(Cfg<ROWS>::kThreads, 1)
@@ -200,26 +80,7 @@ dequant_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *fail = 0;
     }
-    if (tid < 16) {
-        // nibble -> four 16-bit masks (two words).  16 entries x 8 bytes = 128 bytes = one row of
-        // all 32 banks: lanes with different nibbles hit different banks, equal nibbles broadcast.
-        const int e = tid;
-        uint2 v;
-        v.x = ((e & 1) ? 0xffffu : 0u) | ((e & 2) ? 0xffff0000u : 0u);
-        v.y = ((e & 4) ? 0xffffu : 0u) | ((e & 8) ? 0xffff0000u : 0u);
-        lut[e] = v;
-        // q = 2 only: nibble of plane 0 / plane 1 -> one selector byte per weight for prmt:
-        // byte t = 0x10 + 0x22 * bit_t (plane 0), 0x44 * bit_t (plane 1); their OR selects the
-        // fp16 value of index b0 + 2*b1 out of the 8 bytes {v0, v1, v2, v3}
-        uint32_t sa = 0x10101010u, sb = 0u;
-        for (int t2 = 0; t2 < 4; ++t2)
-            if (e >> t2 & 1) {
-                sa += 0x22u << (8 * t2);
-                sb += 0x44u << (8 * t2);
-            }
-        sel_lut[e] = sa;
-        sel_lut[16 + e] = sb;
-    }
+    if (tid < 16) fill_dequant_tables(tid, lut, sel_lut);
     if (warp == 1) {   // tensor memory: 256 fp32 columns x 128 lanes per accumulator
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(C::kTmemCols) : "memory");
@@ -281,67 +142,17 @@ dequant_gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) 
             const int s = kt % kStages;
             if (kt + 1 < ksteps) load_raw<Q>(nxt, a, kt + 1, oct, r, hh, row_ok);
             if (kt >= kStages && !mbar_wait(bar_empty + 8 * s, ((kt / kStages) - 1) & 1)) *fail = 1;
-            uint32_t f[Q][2];                       // [plane][source pair] 16 bits each
+            uint32_t bits[Q];                       // the 32 bits of each plane in source order
 #pragma unroll
-            for (int p = 0; p < Q; ++p) {
-                const uint32_t lo = cur.w[p] & 0xffffu, hi = cur.w[p] >> 16;
-                f[p][0] = swap ? hi : lo;
-                f[p][1] = swap ? lo : hi;
-            }
-            const uint32_t wtile = tiles + s * kStageBytes;
-            if constexpr (Q == 2) {
-                // the four values a weight of this group can take, each rounded once to fp16
-                const float zf = __half2float(__ushort_as_half(cur.z));
-                const float a0 = __half2float(__ushort_as_half(cur.al[0]));
-                const float a1 = __half2float(__ushort_as_half(cur.al[1]));
-                uint32_t t01, t23;
-                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(t01) : "f"(zf + a0), "f"(zf));
-                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(t23) : "f"(zf + a0 + a1), "f"(zf + a1));
+            for (int p = 0; p < Q; ++p) bits[p] = swap ? __funnelshift_l(cur.w[p], cur.w[p], 16) : cur.w[p];
+            uint32_t o[16];
+            dequant_channels<Q, 32>(bits, cur.al, cur.z, lut, sel_lut, o);
+            const uint32_t wrow = tiles + s * kStageBytes + row_smem;
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        uint32_t acc[4];
-#pragma unroll
-                        for (int hn = 0; hn < 2; ++hn) {       // low / high nibble: 4 weights each
-                            const int sh = 8 * b + 4 * hn;
-                            const uint32_t sel = sel_lut[(f[0][i] >> sh) & 0xfu] | sel_lut[16 + ((f[1][i] >> sh) & 0xfu)];
-                            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(acc[2 * hn]) : "r"(t01), "r"(t23), "r"(sel));
-                            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(acc[2 * hn + 1]) : "r"(t01), "r"(t23), "r"(sel >> 16));
-                        }
-                        const int c = 4 * hh + 2 * i + b;
-                        const uint32_t dst = wtile + row_smem + (uint32_t)((c ^ (t & 7)) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(acc[0]), "r"(acc[1]),
-                                     "r"(acc[2]), "r"(acc[3]) : "memory");
-                    }
-                }
-            } else {
-                uint32_t al[Q];                         // fp16x2 alpha per plane
-#pragma unroll
-                for (int p = 0; p < Q; ++p) al[p] = (uint32_t)cur.al[p] * 0x10001u;
-                const uint32_t zz = (uint32_t)cur.z * 0x10001u;
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {              // source pair: channels 32hh + 16i .. +15
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {          // byte b of the pair: 8 channels = one 16-byte chunk
-                        uint32_t acc[4] = {zz, zz, zz, zz};
-#pragma unroll
-                        for (int p = 0; p < Q; ++p) {
-                            const uint2 mlo = lut[(f[p][i] >> (8 * b)) & 0xfu];
-                            const uint2 mhi = lut[(f[p][i] >> (8 * b + 4)) & 0xfu];
-                            const uint32_t mw[4] = {mlo.x, mlo.y, mhi.x, mhi.y};
-#pragma unroll
-                            for (int w2 = 0; w2 < 4; ++w2) {
-                                const uint32_t term = mw[w2] & al[p];
-                                asm("add.rn.f16x2 %0, %0, %1;" : "+r"(acc[w2]) : "r"(term));
-                            }
-                        }
-                        const int c = 4 * hh + 2 * i + b;  // chunk of the 128-byte row, swizzled by the row
-                        const uint32_t dst = wtile + row_smem + (uint32_t)((c ^ (t & 7)) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(acc[0]), "r"(acc[1]),
-                                     "r"(acc[2]), "r"(acc[3]) : "memory");
-                    }
-                }
+            for (int ci = 0; ci < 4; ++ci) {        // 8 channels = one 16-byte chunk, swizzled by the row
+                const uint32_t dst = wrow + (uint32_t)(((4 * hh + ci) ^ (t & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[4 * ci]), "r"(o[4 * ci + 1]),
+                             "r"(o[4 * ci + 2]), "r"(o[4 * ci + 3]) : "memory");
             }
             fence_proxy_async();
             __syncwarp();
@@ -412,24 +223,10 @@ __global__ void bf16_to_f16_kernel(const uint4 *__restrict__ in, uint4 *__restri
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 }  // namespace gemm
+
+// 0 = by the number of tokens, 1 = dequant_gemm_kernel, 2 = dequant_gemm_pair_kernel
+static std::atomic<int> g_prefill_kernel{0};
 
 // Tile shape: rows per CTA (128 or 256) and tokens per CTA (multiple of 32 up to 256), chosen
 // to waste the fewest SM-waves; ties go to the larger tile (less activation traffic from L2).
@@ -494,6 +291,23 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
     }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, w->device);
+    GemmArgs a;
+    a.planes = w->d_planes;
+    a.meta = w->d_meta;
+    a.bias = w->d_bias;
+    a.y = y;
+    a.status = (int *)workspace;
+    a.m = m; a.n = w->n; a.k = w->k; a.np = d.np; a.kp = d.kp; a.octs = d.octs; a.duos = d.duos;
+    a.gpw = d.gpw; a.gshift = d.gshift;
+    a.tile_m = 0;
+    a.y_dtype = y_dtype;
+    // CTA pairs with the weight operand in tensor memory from 128 tokens on (below that the
+    // dequantization of a tile is most of its time in either kernel)
+    const int which = g_prefill_kernel.load(std::memory_order_relaxed);
+    if (which == 2 || (which == 0 && m >= 128)) {
+        const int rc = launch_dequant_gemm_pair(a, w->q, x, sms, stream);
+        if (rc != HLQ_ERR_UNSUPPORTED) return rc;
+    }
     int rows = 128, tile_m = 256;
     choose_tiles(w->n, m, sms, &rows, &tile_m);
 
@@ -507,16 +321,7 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return HLQ_ERR_INVALID_ARGUMENT;
 
-    GemmArgs a;
-    a.planes = w->d_planes;
-    a.meta = w->d_meta;
-    a.bias = w->d_bias;
-    a.y = y;
-    a.status = (int *)workspace;
-    a.m = m; a.n = w->n; a.k = w->k; a.np = d.np; a.kp = d.kp; a.octs = d.octs; a.duos = d.duos;
-    a.gpw = d.gpw; a.gshift = d.gshift;
     a.tile_m = tile_m;
-    a.y_dtype = y_dtype;
     dim3 grid((w->n + rows - 1) / rows, (m + tile_m - 1) / tile_m);
 #define HLQ_GEMM_CASE(R, QV) \
     if (rows == R && w->q == QV) return launch_inst<R, QV>(a, xmap, grid, stream);
@@ -527,3 +332,9 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
 }
 
 }  // namespace hlq
+
+extern "C" int hlq_select_prefill_kernel(int which) {
+    if (which < 0 || which > 2) return HLQ_ERR_INVALID_ARGUMENT;
+    hlq::g_prefill_kernel.store(which, std::memory_order_relaxed);
+    return HLQ_OK;
+}

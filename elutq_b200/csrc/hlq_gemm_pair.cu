@@ -1,0 +1,398 @@
+// Dequantize + tensor-core GEMM over HLQ weights for prefill on CTA PAIRS, sm_100a.
+//
+// Replaces the reference's prefill path, which runs one GEMV per token and re-streams all
+// weights m times (C++/ops/src/arm/arm_gemm.cpp:362-387).  dequant_gemm_kernel (hlq_gemm.cu) moves
+// both operands through shared memory: the dequantizers write the fp16 weight tile there and
+// the tensor cores read it back, which together with the nibble-table lookups keeps the
+// load/store pipe busier than the tensor pipe.  Here the weight operand never touches shared
+// memory, and two CTAs on neighbouring SMs (a cluster of two) share the token tile:
+//   * a pair owns 256 weight rows x up to 256 tokens; CTA c of the pair dequantizes rows
+//     128 c .. 128 c + 127 straight from registers into its own TENSOR MEMORY (tcgen05.st, one
+//     lane = one row, a column = two channels), eight K steps of 64 channels deep;
+//   * each CTA brings in HALF of the token tile of a K step by TMA (128-byte swizzle); the
+//     copies of both CTAs complete on the barrier of CTA 0 (cp.async.bulk.tensor ... cta_group::2);
+//   * one thread of CTA 0 issues tcgen05.mma.cta_group::2 (256 x tokens x 16, A from tensor memory
+//     of both SMs, B from shared memory of both SMs) and commits each stage free in both CTAs;
+//   * both CTAs read their 128 x tokens accumulator back and store y[token][row] (+ bias).
+// Shared memory carries 16 KB per K step and SM, a quarter of the single-CTA kernel's.
+//
+//   warp 0        TMA producer (one thread)
+//   warp 1        tensor memory allocation; in CTA 0 one thread issues the products
+//   warps 4..19   dequantizers, then epilogue: warp w owns lanes 32 (w & 3) .. +31 of tensor
+//                 memory (= rows of the tile) and quarter (w - 4) >> 2 of every slice of 512
+//                 channels, i.e. two of the eight K steps in flight: a lane's unit of work is
+//                 the streaming layout's unit, 16 bytes per plane = 128 channels of a row
+//
+// Precision and operand formats as in hlq_gemm.cu.  All waits are bounded (poll limit); the first
+// that runs out sets the CTA's failure flag, later waits give up at once, both CTAs still meet at
+// the cluster barriers and tensor memory is always released.
+#include <cuda.h>
+
+#include "hlq_gemm_dev.cuh"
+
+namespace hlq {
+namespace gemm {
+
+namespace {
+
+constexpr int kPairStages = 8;                                   // K steps in flight (both operands)
+constexpr int kPairDeqWarps = 16;
+constexpr int kPairThreads = 128 + 32 * kPairDeqWarps;
+constexpr uint32_t kPairXStage = (kMaxTileM / 2) * kTileK * 2;   // 16 KB: half a token tile
+constexpr uint32_t kPairDynSmem = 1024 + kPairStages * kPairXStage + kLutBytes + kBarBytes;
+constexpr uint32_t kPairAccCols = 256, kPairACols = kTileK / 2;  // accumulator; one K step of the weight operand
+constexpr uint32_t kPairTmemCols = 512;
+static_assert(kPairStages == 8, "the ring of K steps is one slice of the streaming layout");
+static_assert(kPairAccCols + kPairStages * kPairACols <= kPairTmemCols, "tensor memory of one SM");
+static_assert(8 * (3 * kPairStages + 1) + 16 <= kBarBytes, "barriers");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t mbar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// false when the wait gave up; once the CTA's flag is set every wait tries once
+__device__ __forceinline__ bool pair_wait(uint32_t mbar, uint32_t parity, volatile int *fail) {
+    if (mbar_try_wait_cluster(mbar, parity)) return true;
+    if (!*fail)
+        for (int i = 0; i < kSpinLimit; ++i) {
+            if (mbar_try_wait_cluster(mbar, parity)) return true;
+            if ((i & 255) == 255 && *fail) break;
+        }
+    *fail = 1;
+    return false;
+}
+// this CTA's half of the token tile; completion is counted on `cluster_mbar` (a barrier of CTA 0)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                                 uint32_t cluster_mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_mbar) : "memory");
+}
+// kind::f16, fp32 accumulator, A and B fp16, both K-major, M = 256 over the pair, N = tokens per tile
+__device__ __forceinline__ uint32_t pair_idesc(int tile_m) {
+    return (1u << 4) | ((uint32_t)(tile_m >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at `cluster_mbar` (of either CTA) once the products issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_mbar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_mbar)
+                 : "memory");
+}
+
+// What a dequantizer thread fetches for one slice of 512 channels: the 16 bytes per plane that hold
+// the 128 channels of its row in its quarter of the slice, and the fp16 scales / zero of the
+// (up to four) groups they fall into, low bits first.
+template <int Q>
+struct RawSlice {
+    uint4 w[Q];
+    uint2 mt[Q + 1];
+};
+// ln = lane of the streaming layout (4 r + quarter)
+template <int Q>
+__device__ __forceinline__ void load_slice(RawSlice<Q> &rw, const GemmArgs &a, int sl, int oct, int ln, bool row_ok) {
+#pragma unroll
+    for (int p = 0; p < Q; ++p) {
+        rw.w[p] = make_uint4(0u, 0u, 0u, 0u);
+        if (row_ok)
+            rw.w[p] = __ldg((const uint4 *)(a.planes + (((int64_t)sl * a.octs + oct) * Q + p) * kCellBytes + ln * 16));
+    }
+#pragma unroll
+    for (int p = 0; p <= Q; ++p) {
+        const uint16_t *mp = a.meta + (((((int64_t)sl * a.duos + (oct >> 1)) * (Q + 1) + p) * 32 + ln) * 2 + (oct & 1)) * a.gpw;
+        rw.mt[p] = make_uint2(0u, 0u);
+        if (row_ok) {
+            if (a.gpw == 4) rw.mt[p] = __ldg((const uint2 *)mp);
+            else if (a.gpw == 2) rw.mt[p].x = __ldg((const uint32_t *)mp);
+            else rw.mt[p].x = __ldg(mp);
+        }
+    }
+}
+// the four words of a plane in source order: byte pair s of the lane's 16 bytes is stored at s ^ r
+__device__ __forceinline__ void source_words(const uint4 &w, int r, uint32_t (&o)[4]) {
+    uint32_t w0 = w.x, w1 = w.y, w2 = w.z, w3 = w.w, t;
+    if (r & 2) { t = w0; w0 = w1; w1 = t; t = w2; w2 = w3; w3 = t; }
+    if (r & 4) { t = w0; w0 = w2; w2 = t; t = w1; w1 = w3; w3 = t; }
+    if (r & 1) {
+        w0 = __funnelshift_l(w0, w0, 16); w1 = __funnelshift_l(w1, w1, 16);
+        w2 = __funnelshift_l(w2, w2, 16); w3 = __funnelshift_l(w3, w3, 16);
+    }
+    o[0] = w0; o[1] = w1; o[2] = w2; o[3] = w3;
+}
+
+template <int Q>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t sbase = smem_u32(smem_raw);
+    const uint32_t tiles = (sbase + 1023u) & ~1023u;          // operand tiles need 1024-byte alignment
+    unsigned char *tiles_ptr = smem_raw + (tiles - sbase);
+    const uint32_t lut_u32 = tiles + kPairStages * kPairXStage;
+    uint2 *lut = (uint2 *)(tiles_ptr + kPairStages * kPairXStage);
+    uint32_t *sel_lut = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + 128);   // 2 x 16 words
+    const uint32_t bars = lut_u32 + kLutBytes;
+    // barriers: full_x[s], full_w[s] (waited for in CTA 0 only), empty[s], acc_full; TMEM base; flag
+    const uint32_t bar_full_x = bars, bar_full_w = bars + 8 * kPairStages, bar_empty = bars + 16 * kPairStages;
+    const uint32_t bar_acc = bars + 24 * kPairStages;
+    uint32_t *tmem_slot = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + kLutBytes + 24 * kPairStages + 8);
+    volatile int *fail = (volatile int *)(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_rank();                     // 0: issues the products
+    const int n0 = (int)(blockIdx.x >> 1) * 256 + 128 * (int)rank;
+    const int m0 = blockIdx.y * a.tile_m;
+    const int half_m = a.tile_m >> 1;                         // tokens this CTA brings in
+    const int ksteps = a.kp / kTileK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            mbar_init(bar_full_x + 8 * s, 1);
+            mbar_init(bar_full_w + 8 * s, 2 * 4);               // the four warps of a quarter of the slice, both CTAs
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *fail = 0;
+    }
+    if (tid < 16) fill_dequant_tables(tid, lut, sel_lut);
+    if (warp == 1) {   // all of tensor memory, in both CTAs with one instruction each
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kPairTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // barriers of CTA 0 as seen from here
+    const uint32_t lead_full_x = map_to_cta(bar_full_x, 0), lead_full_w = map_to_cta(bar_full_w, 0);
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer --------------------------------------
+        if (lane == 0) {
+            const uint32_t xbytes = (uint32_t)a.tile_m * kTileK * 2;      // both halves
+            for (int kt = 0; kt < ksteps; ++kt) {
+                const int s = kt % kPairStages;
+                if (kt >= kPairStages && !pair_wait(bar_empty + 8 * s, ((kt / kPairStages) - 1) & 1, fail)) break;
+                if (rank == 0) mbar_expect_tx(bar_full_x + 8 * s, xbytes);
+                tma_load_2d_pair(tiles + s * kPairXStage, &xmap, kt * kTileK, m0 + (int)rank * half_m,
+                                 lead_full_x + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ----------------------------------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = pair_idesc(a.tile_m);
+            const uint32_t peer_empty = map_to_cta(bar_empty, 1);
+            bool ok = true;
+            for (int kt = 0; kt < ksteps && ok; ++kt) {
+                const int s = kt % kPairStages;
+                const uint32_t ph = (kt / kPairStages) & 1;
+                ok = pair_wait(bar_full_x + 8 * s, ph, fail) && pair_wait(bar_full_w + 8 * s, ph, fail);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t bdesc = umma_desc(tiles + s * kPairXStage);
+                const uint32_t acol = tmem_base + kPairAccCols + (uint32_t)s * kPairACols;
+#pragma unroll
+                for (int kk = 0; kk < kTileK / 16; ++kk)     // 16 channels = 8 columns of A, 32 bytes of B
+                    umma_f16_ts_pair(tmem_base, acol + 8 * kk, bdesc + 2 * kk, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+                umma_commit_pair(bar_empty + 8 * s);           // the stage is free again, in both CTAs
+                umma_commit_pair(peer_empty + 8 * s);
+            }
+            // also after a wait that gave up: the products issued so far end, both CTAs' epilogues wake
+            umma_commit_pair(bar_acc);
+            umma_commit_pair(map_to_cta(bar_acc, 1));
+        }
+    } else if (warp >= 4) {
+        // ------------------------------ dequantizers --------------------------------------
+        const int wd = warp - 4;
+        const int q4 = warp & 3;                 // lanes 32 q4 .. +31 of tensor memory belong to this warp
+        const int part = wd >> 2;                // quarter of every slice: K steps 2 part and 2 part + 1 of its eight
+        const int t = 32 * q4 + lane;            // weight row inside this CTA's half of the tile
+        const int n = n0 + t;
+        const bool row_ok = n < a.np;
+        const int oct = n >> 3, r = n & 7, ln = 4 * r + part;
+        const uint32_t tlane = tmem_base + ((uint32_t)(32 * q4) << 16) + kPairAccCols;
+        const int slices = ksteps >> 3;
+        const int gsel = r >> a.gshift;          // stored group u holds source group u ^ gsel
+        RawSlice<Q> cur, nxt;
+        load_slice<Q>(cur, a, 0, oct, ln, row_ok);
+        bool ok = true;
+        for (int sl = 0; sl < slices && ok; ++sl) {
+            if (sl + 1 < slices) load_slice<Q>(nxt, a, sl + 1, oct, ln, row_ok);
+            uint32_t src[Q][4];
+#pragma unroll
+            for (int p = 0; p < Q; ++p) source_words(cur.w[p], r, src[p]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int s = 2 * part + h;       // K step 8 sl + s lives in stage s: the ring is one slice deep
+                if (sl >= 1) ok = pair_wait(bar_empty + 8 * s, (uint32_t)(sl - 1) & 1u, fail);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int w2 = 0; w2 < 2; ++w2) {
+                    const int ws = 2 * h + w2;                            // 32 channels of the lane's 128
+                    const int u = ((ws * a.gpw) >> 2) ^ gsel;
+                    uint32_t bits[Q];
+                    uint16_t al[Q];
+#pragma unroll
+                    for (int p = 0; p < Q; ++p) {
+                        bits[p] = src[p][ws];
+                        al[p] = (uint16_t)((((uint64_t)cur.mt[p].y << 32 | cur.mt[p].x) >> (16 * u)) & 0xffffu);
+                    }
+                    const uint16_t z = (uint16_t)((((uint64_t)cur.mt[Q].y << 32 | cur.mt[Q].x) >> (16 * u)) & 0xffffu);
+                    uint32_t o[16];
+                    dequant_channels<Q, 32>(bits, al, z, lut, sel_lut, o);
+                    asm volatile(
+                        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                        ::"r"(tlane + (uint32_t)s * kPairACols + (uint32_t)(16 * w2)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]),
+                          "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]), "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]),
+                          "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(lead_full_w + 8 * s);
+            }
+            cur = nxt;
+        }
+        // ------------------------------ epilogue ------------------------------------------
+        pair_wait(bar_acc, 0, fail);
+        tc_fence_after();
+        const int row = n0 + t;
+        float bv = 0.f;
+        if (a.bias && row < a.n) bv = __half2float(__ushort_as_half(a.bias[row]));
+        for (int c0 = 32 * part; c0 < a.tile_m; c0 += 32 * (kPairDeqWarps / 4)) {
+            uint32_t v[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+                  "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+                  "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+                  "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < a.n && !*fail) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int tok = m0 + c0 + c;
+                    if (tok < a.m) {
+                        const float o = __uint_as_float(v[c]) + bv;
+                        const int64_t idx = (int64_t)tok * a.n + row;
+                        if (a.y_dtype == HLQ_F16) ((__half *)a.y)[idx] = __float2half_rn(o);
+                        else if (a.y_dtype == HLQ_BF16) ((__nv_bfloat16 *)a.y)[idx] = __float2bfloat16_rn(o);
+                        else ((float *)a.y)[idx] = o;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // nothing of the peer still arrives here or reads this CTA's operands
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kPairTmemCols)
+                     : "memory");
+    }
+    if (tid == 0 && *fail) atomicExch(a.status, 1);
+}
+
+template <int Q>
+int launch_pair_inst(const GemmArgs &a, const CUtensorMap &xmap, dim3 grid, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    HLQ_CUDA(cudaGetDevice(&dev));
+    auto kernel = dequant_gemm_pair_kernel<Q>;
+    if (!configured[dev & 63]) {
+        HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairDynSmem));
+        configured[dev & 63] = true;
+    }
+    kernel<<<grid, kPairThreads, kPairDynSmem, stream>>>(a, xmap);
+    count_launch();
+    return note_cuda(cudaGetLastError());
+}
+
+}  // namespace
+
+// Tokens per pair tile: a multiple of 32 from 128 to 256 that wastes the fewest waves of SM pairs.
+int pair_tile_tokens(int n, int m, int sms, double *cost) {
+    const int pairs = sms / 2 > 0 ? sms / 2 : 1;
+    double best = 1e300;
+    int tile = 256;
+    const int lo = m >= 128 ? 128 : ((m + 31) / 32 * 32);
+    for (int tm = 256; tm >= lo; tm -= 32) {
+        const long long tiles = (long long)((n + 255) / 256) * ((m + tm - 1) / tm);
+        const long long waves = (tiles + pairs - 1) / pairs;
+        const double c = (double)waves * tm;
+        if (c < best * 0.999) {
+            best = c;
+            tile = tm;
+        }
+    }
+    if (cost) *cost = best;
+    return tile;
+}
+
+int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms, cudaStream_t stream) {
+    if (a_in.m < 64 || sms < 2) return HLQ_ERR_UNSUPPORTED;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return HLQ_ERR_NO_DEVICE;
+    GemmArgs a = a_in;
+    a.tile_m = pair_tile_tokens(a.n, a.m, sms, nullptr);
+    CUtensorMap xmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)(a.tile_m / 2)};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return HLQ_ERR_INVALID_ARGUMENT;
+    dim3 grid(2 * ((a.n + 255) / 256), (a.m + a.tile_m - 1) / a.tile_m);
+    if (grid.y > 65535) return HLQ_ERR_UNSUPPORTED;
+    switch (q) {
+        case 1: return launch_pair_inst<1>(a, xmap, grid, stream);
+        case 2: return launch_pair_inst<2>(a, xmap, grid, stream);
+        case 3: return launch_pair_inst<3>(a, xmap, grid, stream);
+        case 4: return launch_pair_inst<4>(a, xmap, grid, stream);
+    }
+    return HLQ_ERR_SHAPE;
+}
+
+}  // namespace gemm
+}  // namespace hlq
