@@ -33,18 +33,28 @@
 namespace hlq {
 namespace gemm {
 
+#ifdef GP_TRACE
+__device__ long long g_trace_mma[8192];
+__device__ long long g_trace_deq[8192];
+#define GP_T(buf, idx) do { if (pair == 0 && (idx) < 8192) buf[idx] = clock64(); } while (0)
+#else
+#define GP_T(buf, idx) do { } while (0)
+#endif
+
 namespace {
 
-constexpr int kPairStages = 8;                                   // K steps in flight (both operands)
+constexpr int kPairStepK = 128;                                  // channels per K step: a quarter of a slice
+constexpr int kPairStages = 4;                                   // K steps in flight (both operands): one slice
 constexpr int kPairDeqWarps = 16;
 constexpr int kPairThreads = 128 + 32 * kPairDeqWarps;
-constexpr uint32_t kPairXStage = (kMaxTileM / 2) * kTileK * 2;   // 16 KB: half a token tile
+constexpr uint32_t kPairXBox = (kMaxTileM / 2) * kTileK * 2;     // 16 KB: half a token tile x 64 channels (one TMA box)
+constexpr uint32_t kPairXStage = 2 * kPairXBox;                  // two boxes: 128 channels
 constexpr uint32_t kPairDynSmem = 1024 + kPairStages * kPairXStage + kLutBytes + kBarBytes;
-constexpr uint32_t kPairAccCols = 256, kPairACols = kTileK / 2;  // accumulator; one K step of the weight operand
+constexpr uint32_t kPairAccCols = 256, kPairACols = kPairStepK / 2;   // accumulator; one K step of the weight operand
 constexpr uint32_t kPairTmemCols = 512;
-static_assert(kPairStages == 8, "the ring of K steps is one slice of the streaming layout");
+static_assert(kPairStages * kPairStepK == 512, "the ring of K steps is one slice of the streaming layout");
 static_assert(kPairAccCols + kPairStages * kPairACols <= kPairTmemCols, "tensor memory of one SM");
-static_assert(8 * (3 * kPairStages + 1) + 16 <= kBarBytes, "barriers");
+static_assert(8 * (2 * kPairStages + 2) + 16 <= kBarBytes, "barriers");
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -61,23 +71,14 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t mbar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
-    return ok != 0;
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // false when the wait gave up; once the CTA's flag is set every wait tries once
 __device__ __forceinline__ bool pair_wait(uint32_t mbar, uint32_t parity, volatile int *fail) {
-    if (mbar_try_wait_cluster(mbar, parity)) return true;
+    if (mbar_try_wait(mbar, parity)) return true;
     if (!*fail)
         for (int i = 0; i < kSpinLimit; ++i) {
-            if (mbar_try_wait_cluster(mbar, parity)) return true;
+            if (mbar_try_wait(mbar, parity)) return true;
             if ((i & 255) == 255 && *fail) break;
         }
     *fail = 1;
@@ -159,26 +160,30 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
     uint2 *lut = (uint2 *)(tiles_ptr + kPairStages * kPairXStage);
     uint32_t *sel_lut = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + 128);   // 2 x 16 words
     const uint32_t bars = lut_u32 + kLutBytes;
-    // barriers: full_x[s], full_w[s] (waited for in CTA 0 only), empty[s], acc_full; TMEM base; flag
-    const uint32_t bar_full_x = bars, bar_full_w = bars + 8 * kPairStages, bar_empty = bars + 16 * kPairStages;
-    const uint32_t bar_acc = bars + 24 * kPairStages;
-    uint32_t *tmem_slot = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + kLutBytes + 24 * kPairStages + 8);
+    // barriers: full[s] and acc_empty (waited for in CTA 0 only), empty[s], acc_full; TMEM base; flag.
+    // full[s] counts both operands of a K step: the token tile's bytes of both CTAs (announced by
+    // CTA 0's producer) and one arrival per dequantizer warp that wrote its rows, so that the
+    // issuing thread waits once per step.
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * kPairStages;
+    const uint32_t bar_acc = bars + 16 * kPairStages, bar_acc_empty = bar_acc + 8;
+    uint32_t *tmem_slot = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + kLutBytes + 16 * kPairStages + 16);
     volatile int *fail = (volatile int *)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_rank();                     // 0: issues the products
-    const int n0 = (int)(blockIdx.x >> 1) * 256 + 128 * (int)rank;
-    const int m0 = blockIdx.y * a.tile_m;
+    const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
     const int half_m = a.tile_m >> 1;                         // tokens this CTA brings in
-    const int ksteps = a.kp / kTileK;
+    const int ksteps = a.kp / kPairStepK;                     // a multiple of 4: the streaming layout pads K to 512
+    const int tok_tiles = (a.m + a.tile_m - 1) / a.tile_m;
+    const int ntiles = ((a.n + 255) / 256) * tok_tiles;       // tile = (256 rows) x (tile_m tokens), tokens fastest
 
     if (tid == 0) {
         for (int s = 0; s < kPairStages; ++s) {
-            mbar_init(bar_full_x + 8 * s, 1);
-            mbar_init(bar_full_w + 8 * s, 2 * 4);               // the four warps of a quarter of the slice, both CTAs
+            mbar_init(bar_full + 8 * s, 1 + 2 * 4);             // producer of CTA 0; the four warps of the step, both CTAs
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_acc, 1);
+        mbar_init(bar_acc_empty, 2 * kPairDeqWarps);            // every epilogue warp of both CTAs
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *fail = 0;
     }
@@ -194,119 +199,111 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // barriers of CTA 0 as seen from here
-    const uint32_t lead_full_x = map_to_cta(bar_full_x, 0), lead_full_w = map_to_cta(bar_full_w, 0);
+    const uint32_t lead_full = map_to_cta(bar_full, 0);
+    const uint32_t lead_acc_empty = map_to_cta(bar_acc_empty, 0);
 
+    // The pair walks its tiles pair, pair + npairs, ...; K steps are counted over all of them (g), so
+    // the ring of four stages and the barrier phases run on across tile boundaries: while the
+    // accumulator of a tile is read back, the operands of the next tile's first K steps are
+    // already being made.
     if (warp == 0) {
         // ------------------------------ TMA producer --------------------------------------
         if (lane == 0) {
-            const uint32_t xbytes = (uint32_t)a.tile_m * kTileK * 2;      // both halves
-            for (int kt = 0; kt < ksteps; ++kt) {
-                const int s = kt % kPairStages;
-                if (kt >= kPairStages && !pair_wait(bar_empty + 8 * s, ((kt / kPairStages) - 1) & 1, fail)) break;
-                if (rank == 0) mbar_expect_tx(bar_full_x + 8 * s, xbytes);
-                tma_load_2d_pair(tiles + s * kPairXStage, &xmap, kt * kTileK, m0 + (int)rank * half_m,
-                                 lead_full_x + 8 * s);
+            const uint32_t xbytes = (uint32_t)a.tile_m * kPairStepK * 2;  // both halves, both boxes
+            int g = 0;
+            bool ok = true;
+            for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+                const int m0 = (tile % tok_tiles) * a.tile_m;
+                for (int kt = 0; kt < ksteps; ++kt, ++g) {
+                    const int s = g % kPairStages;
+                    if (g >= kPairStages) ok = pair_wait(bar_empty + 8 * s, ((g / kPairStages) - 1) & 1, fail);
+                    if (!ok) break;
+                    if (rank == 0) mbar_expect_tx(bar_full + 8 * s, xbytes);
+#pragma unroll
+                    for (int bx = 0; bx < 2; ++bx)
+                        tma_load_2d_pair(tiles + s * kPairXStage + bx * kPairXBox, &xmap, kt * kPairStepK + bx * kTileK,
+                                         m0 + (int)rank * half_m, lead_full + 8 * s);
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ----------------------------------------
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = pair_idesc(a.tile_m);
-            const uint32_t peer_empty = map_to_cta(bar_empty, 1);
+            const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_acc = map_to_cta(bar_acc, 1);
+            int g = 0, it = 0;
             bool ok = true;
-            for (int kt = 0; kt < ksteps && ok; ++kt) {
-                const int s = kt % kPairStages;
-                const uint32_t ph = (kt / kPairStages) & 1;
-                ok = pair_wait(bar_full_x + 8 * s, ph, fail) && pair_wait(bar_full_w + 8 * s, ph, fail);
+            for (int tile = pair; tile < ntiles && ok; tile += npairs, ++it) {
+                // the accumulator of the tile before has been read back by both CTAs
+                if (it >= 1) ok = pair_wait(bar_acc_empty, (uint32_t)(it - 1) & 1u, fail);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t bdesc = umma_desc(tiles + s * kPairXStage);
-                const uint32_t acol = tmem_base + kPairAccCols + (uint32_t)s * kPairACols;
+                for (int kt = 0; kt < ksteps; ++kt, ++g) {
+                    const int s = g % kPairStages;
+                    const uint32_t ph = (g / kPairStages) & 1;
+                    GP_T(g_trace_mma, 4 * g);
+                    ok = pair_wait(bar_full + 8 * s, ph, fail);
+                    GP_T(g_trace_mma, 4 * g + 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t bdesc = umma_desc(tiles + s * kPairXStage);
+                    const uint32_t acol = tmem_base + kPairAccCols + (uint32_t)s * kPairACols;
 #pragma unroll
-                for (int kk = 0; kk < kTileK / 16; ++kk)     // 16 channels = 8 columns of A, 32 bytes of B
-                    umma_f16_ts_pair(tmem_base, acol + 8 * kk, bdesc + 2 * kk, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
-                umma_commit_pair(bar_empty + 8 * s);           // the stage is free again, in both CTAs
-                umma_commit_pair(peer_empty + 8 * s);
+                    for (int kk = 0; kk < kPairStepK / 16; ++kk)    // 16 channels = 8 columns of A, 32 bytes of B
+                        umma_f16_ts_pair(tmem_base, acol + 8 * kk, bdesc + (uint64_t)((kk >> 2) * (kPairXBox >> 4) + 2 * (kk & 3)),
+                                         idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit_pair(bar_empty + 8 * s);           // the stage is free again, in both CTAs
+                    umma_commit_pair(peer_empty + 8 * s);
+                    GP_T(g_trace_mma, 4 * g + 3);
+                }
+                // also after a wait that gave up: the products issued so far end, both CTAs' epilogues wake
+                umma_commit_pair(bar_acc);
+                umma_commit_pair(peer_acc);
             }
-            // also after a wait that gave up: the products issued so far end, both CTAs' epilogues wake
-            umma_commit_pair(bar_acc);
-            umma_commit_pair(map_to_cta(bar_acc, 1));
         }
     } else if (warp >= 4) {
         // ------------------------------ dequantizers --------------------------------------
         const int wd = warp - 4;
         const int q4 = warp & 3;                 // lanes 32 q4 .. +31 of tensor memory belong to this warp
-        const int part = wd >> 2;                // quarter of every slice: K steps 2 part and 2 part + 1 of its eight
+        const int part = wd >> 2;                // quarter of every slice = K step `part` of its four = stage `part`
         const int t = 32 * q4 + lane;            // weight row inside this CTA's half of the tile
-        const int n = n0 + t;
-        const bool row_ok = n < a.np;
-        const int oct = n >> 3, r = n & 7, ln = 4 * r + part;
-        const uint32_t tlane = tmem_base + ((uint32_t)(32 * q4) << 16) + kPairAccCols;
-        const int slices = ksteps >> 3;
-        const int gsel = r >> a.gshift;          // stored group u holds source group u ^ gsel
-        RawSlice<Q> cur, nxt;
-        load_slice<Q>(cur, a, 0, oct, ln, row_ok);
-        bool ok = true;
-        for (int sl = 0; sl < slices && ok; ++sl) {
-            if (sl + 1 < slices) load_slice<Q>(nxt, a, sl + 1, oct, ln, row_ok);
-            uint32_t src[Q][4];
-#pragma unroll
-            for (int p = 0; p < Q; ++p) source_words(cur.w[p], r, src[p]);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int s = 2 * part + h;       // K step 8 sl + s lives in stage s: the ring is one slice deep
-                if (sl >= 1) ok = pair_wait(bar_empty + 8 * s, (uint32_t)(sl - 1) & 1u, fail);
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll
-                for (int w2 = 0; w2 < 2; ++w2) {
-                    const int ws = 2 * h + w2;                            // 32 channels of the lane's 128
-                    const int u = ((ws * a.gpw) >> 2) ^ gsel;
-                    uint32_t bits[Q];
-                    uint16_t al[Q];
-#pragma unroll
-                    for (int p = 0; p < Q; ++p) {
-                        bits[p] = src[p][ws];
-                        al[p] = (uint16_t)((((uint64_t)cur.mt[p].y << 32 | cur.mt[p].x) >> (16 * u)) & 0xffffu);
-                    }
-                    const uint16_t z = (uint16_t)((((uint64_t)cur.mt[Q].y << 32 | cur.mt[Q].x) >> (16 * u)) & 0xffffu);
-                    uint32_t o[16];
-                    dequant_channels<Q, 32>(bits, al, z, lut, sel_lut, o);
-                    asm volatile(
-                        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                        ::"r"(tlane + (uint32_t)s * kPairACols + (uint32_t)(16 * w2)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]),
-                          "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]), "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]),
-                          "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
-                }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        const uint32_t tlane = tmem_base + ((uint32_t)(32 * q4) << 16);
+        const int slices = ksteps >> 2;
+
+        // the accumulator of a finished tile: read back, + bias, stored as y[token][row]
+        auto epilogue = [&](int tile, uint32_t parity) {
+            const int row = (tile / tok_tiles) * 256 + 128 * (int)rank + t;
+            const int m0 = (tile % tok_tiles) * a.tile_m;
+            pair_wait(bar_acc, parity, fail);
+            tc_fence_after();
+            float bv = 0.f;
+            if (a.bias && row < a.n) bv = __half2float(__ushort_as_half(a.bias[row]));
+            const bool good = row < a.n && !*fail;
+            // tells CTA 0 that this warp has read its part: the next tile's products may overwrite it
+            auto release = [&]() {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(lead_full_w + 8 * s);
-            }
-            cur = nxt;
-        }
-        // ------------------------------ epilogue ------------------------------------------
-        pair_wait(bar_acc, 0, fail);
-        tc_fence_after();
-        const int row = n0 + t;
-        float bv = 0.f;
-        if (a.bias && row < a.n) bv = __half2float(__ushort_as_half(a.bias[row]));
-        for (int c0 = 32 * part; c0 < a.tile_m; c0 += 32 * (kPairDeqWarps / 4)) {
+                if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+            };
+            // This warp's columns are at most two chunks of 32.  The accumulator is handed back as soon
+            // as the second chunk is in registers; for 16-bit outputs the first chunk waits there as
+            // finished, packed values, so that nothing is stored before the hand-back.
+            const int c00 = 32 * part, c01 = c00 + 32 * (kPairDeqWarps / 4);
             uint32_t v[32];
-            const uint32_t taddr = tmem_base + ((uint32_t)(32 * q4) << 16) + (uint32_t)c0;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-                  "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-                  "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-                  "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                : "r"(taddr) : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row < a.n && !*fail) {
+            auto load32 = [&](int c0) {
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+                      "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+                      "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+                      "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(tlane + (uint32_t)c0) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            };
+            auto store32 = [&](int c0) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const int tok = m0 + c0 + c;
@@ -318,8 +315,130 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                         else ((float *)a.y)[idx] = o;
                     }
                 }
+            };
+            if (c00 >= a.tile_m) {                       // a narrow tile leaves this warp nothing
+                release();
+            } else if (c01 >= a.tile_m) {                // one chunk
+                load32(c00);
+                release();
+                if (good) store32(c00);
+            } else if (a.y_dtype == HLQ_F32) {           // two chunks of fp32 outputs: no room to keep the first
+                load32(c00);
+                if (good) store32(c00);
+                load32(c01);
+                release();
+                if (good) store32(c01);
+            } else {
+                load32(c00);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float lo = __uint_as_float(v[2 * i]) + bv, hi = __uint_as_float(v[2 * i + 1]) + bv;
+                    if (a.y_dtype == HLQ_F16) {
+                        const __half2 h2 = __floats2half2_rn(lo, hi);
+                        pk[i] = *(const uint32_t *)&h2;
+                    } else {
+                        const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                        pk[i] = *(const uint32_t *)&b2;
+                    }
+                }
+                load32(c01);
+                release();
+                if (good) {
+                    store32(c01);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int tok = m0 + c00 + c;
+                        if (tok < a.m) ((uint16_t *)a.y)[(int64_t)tok * a.n + row] = (uint16_t)(pk[c >> 1] >> (16 * (c & 1)));
+                    }
+                }
             }
+        };
+
+        RawSlice<Q> cur, nxt;
+        int n = (pair / tok_tiles) * 256 + 128 * (int)rank + t;
+        if (pair < ntiles) load_slice<Q>(cur, a, 0, n >> 3, 4 * (n & 7) + part, n < a.np);
+        int gs = 0, it = 0;                      // slices and tiles so far
+        int pending = -1;                        // tile whose accumulator is still to be read back
+        bool ok = true;
+        for (int tile = pair; tile < ntiles && ok; tile += npairs, ++it) {
+            const int r = n & 7;
+            const int gsel = r >> a.gshift;      // stored group u holds source group u ^ gsel
+            for (int sl = 0; sl < slices && ok; ++sl, ++gs) {
+                // the next slice of this tile, else the first slice of the next tile
+                {
+                    int nn = n, nsl = sl + 1;
+                    if (nsl == slices) {
+                        nsl = 0;
+                        nn = ((tile + npairs) / tok_tiles) * 256 + 128 * (int)rank + t;
+                    }
+                    if (nsl > 0 || tile + npairs < ntiles) load_slice<Q>(nxt, a, nsl, nn >> 3, 4 * (nn & 7) + part, nn < a.np);
+                }
+                if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs);
+                uint32_t src[Q][4];
+#pragma unroll
+                for (int p = 0; p < Q; ++p) source_words(cur.w[p], r, src[p]);
+                // K step 4 gs + part lives in stage `part`: the ring is one slice deep.  Half of the
+                // weights are made before the wait for the stage (it is busy for as long as the products
+                // that read it, and the arithmetic need not wait for them), the other half after.
+                const int s = part;
+                auto make = [&](int ws, uint32_t (&o)[16]) {                  // 32 channels of the lane's 128
+                    const int u = ((ws * a.gpw) >> 2) ^ gsel;
+                    uint32_t bits[Q];
+                    uint16_t al[Q];
+#pragma unroll
+                    for (int p = 0; p < Q; ++p) {
+                        bits[p] = src[p][ws];
+                        al[p] = (uint16_t)((((uint64_t)cur.mt[p].y << 32 | cur.mt[p].x) >> (16 * u)) & 0xffffu);
+                    }
+                    const uint16_t z = (uint16_t)((((uint64_t)cur.mt[Q].y << 32 | cur.mt[Q].x) >> (16 * u)) & 0xffffu);
+                    dequant_channels<Q, 32>(bits, al, z, lut, sel_lut, o);
+                };
+                auto put = [&](int ws, const uint32_t (&o)[16]) {
+                    asm volatile(
+                        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                        ::"r"(tlane + kPairAccCols + (uint32_t)s * kPairACols + (uint32_t)(16 * ws)), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                          "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]), "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]),
+                          "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+                };
+                {
+                    uint32_t o0[16], o1[16];
+                    make(0, o0);
+                    make(1, o1);
+                    if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 1);
+                    if (gs >= 1) ok = pair_wait(bar_empty + 8 * s, (uint32_t)(gs - 1) & 1u, fail);
+                    if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    put(0, o0);
+                    put(1, o1);
+                }
+                {
+                    uint32_t o2[16], o3[16];
+                    make(2, o2);
+                    put(2, o2);
+                    make(3, o3);
+                    put(3, o3);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(lead_full + 8 * s);
+                if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 3);
+                cur = nxt;
+                if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 7);
+                // the tile before: its accumulator is read back once this tile's first operands are on
+                // their way, so that the tensor cores wait for the read-back alone
+                if (sl == 0 && pending >= 0 && ok) {
+                    epilogue(pending, (uint32_t)(it - 1) & 1u);
+                    pending = -1;
+                }
+            }
+            pending = tile;
+            n = ((tile + npairs) / tok_tiles) * 256 + 128 * (int)rank + t;
         }
+        if (pending >= 0) epilogue(pending, (uint32_t)(it - 1) & 1u);
     }
     tc_fence_before();
     __syncthreads();
@@ -333,16 +452,32 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
 }
 
 template <int Q>
-int launch_pair_inst(const GemmArgs &a, const CUtensorMap &xmap, dim3 grid, cudaStream_t stream) {
-    static bool configured[64] = {};
+int launch_pair_inst(const GemmArgs &a, const CUtensorMap &xmap, int ntiles, cudaStream_t stream) {
+    static int pairs_cached[64] = {};        // clusters of two that run at once, per device; 0 = not asked yet
     int dev = 0;
     HLQ_CUDA(cudaGetDevice(&dev));
     auto kernel = dequant_gemm_pair_kernel<Q>;
-    if (!configured[dev & 63]) {
+    int &pairs = pairs_cached[dev & 63];
+    if (pairs == 0) {
         HLQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairDynSmem));
-        configured[dev & 63] = true;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 1024);
+        cfg.blockDim = dim3(kPairThreads);
+        cfg.dynamicSmemBytes = kPairDynSmem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int nclusters = 0;
+        HLQ_CUDA(cudaOccupancyMaxActiveClusters(&nclusters, kernel, &cfg));
+        if (nclusters < 1) return HLQ_ERR_UNSUPPORTED;
+        pairs = nclusters;
     }
-    kernel<<<grid, kPairThreads, kPairDynSmem, stream>>>(a, xmap);
+    const int use = ntiles < pairs ? ntiles : pairs;
+    kernel<<<2 * use, kPairThreads, kPairDynSmem, stream>>>(a, xmap);
     count_launch();
     return note_cuda(cudaGetLastError());
 }
@@ -383,16 +518,23 @@ int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return HLQ_ERR_INVALID_ARGUMENT;
-    dim3 grid(2 * ((a.n + 255) / 256), (a.m + a.tile_m - 1) / a.tile_m);
-    if (grid.y > 65535) return HLQ_ERR_UNSUPPORTED;
+    const int ntiles = ((a.n + 255) / 256) * ((a.m + a.tile_m - 1) / a.tile_m);
     switch (q) {
-        case 1: return launch_pair_inst<1>(a, xmap, grid, stream);
-        case 2: return launch_pair_inst<2>(a, xmap, grid, stream);
-        case 3: return launch_pair_inst<3>(a, xmap, grid, stream);
-        case 4: return launch_pair_inst<4>(a, xmap, grid, stream);
+        case 1: return launch_pair_inst<1>(a, xmap, ntiles, stream);
+        case 2: return launch_pair_inst<2>(a, xmap, ntiles, stream);
+        case 3: return launch_pair_inst<3>(a, xmap, ntiles, stream);
+        case 4: return launch_pair_inst<4>(a, xmap, ntiles, stream);
     }
     return HLQ_ERR_SHAPE;
 }
 
 }  // namespace gemm
 }  // namespace hlq
+
+#ifdef GP_TRACE
+extern "C" int hlq_dbg_pair_trace(long long *mma, long long *deq) {
+    cudaMemcpyFromSymbol(mma, hlq::gemm::g_trace_mma, sizeof(long long) * 8192);
+    cudaMemcpyFromSymbol(deq, hlq::gemm::g_trace_deq, sizeof(long long) * 8192);
+    return 0;
+}
+#endif
