@@ -530,7 +530,7 @@ def prefill_object(dev, args, layers, steps, warmup):
             "value": tf, "unit": "TFLOP/s", "ms_per_step": sec * 1e3, "steps": steps,
             "frac_of_sustained_bf16": tf / peaks["tf_sustained"], "frac_of_burst_bf16": tf / peaks["tf_burst"],
             "peaks": {"sustained": peaks["tf_sustained"], "burst": peaks["tf_burst"], "source": peaks["kind"]},
-            "launches_per_step": int(launches), "kernel": "dequant_gemm_kernel",
+            "launches_per_step": int(launches), "kernel": "dequant_gemm_pair_kernel",
             "dtype": "fp16 operands (weights dequantized to fp16, bf16 tokens converted), f32 accumulate",
             "clocks": merge_clocks(clocks)}
 
@@ -764,7 +764,7 @@ def run_prefill(args):
         "gpu_launches": int(p["launches_per_step"] * args.steps * 3), "clocks": p["clocks"],
         "roofline": {"bound": "tensor", "achieved": p["value"], "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
                      "frac": p["frac_of_sustained_bf16"], "frac_of_burst": p["frac_of_burst_bf16"], "traffic": None,
-                     "peak_source": f"of {peaks['kind']}, sustained", "kernel": "dequant_gemm_kernel"}}), flush=True)
+                     "peak_source": f"of {peaks['kind']}, sustained", "kernel": "dequant_gemm_pair_kernel"}}), flush=True)
 
 
 def main():

@@ -225,7 +225,7 @@ __global__ void bf16_to_f16_kernel(const uint4 *__restrict__ in, uint4 *__restri
 
 }  // namespace gemm
 
-// 0 = by the number of tokens, 1 = dequant_gemm_kernel, 2 = dequant_gemm_pair_kernel
+// 0 or 2 = dequant_gemm_pair_kernel, 1 = dequant_gemm_kernel
 static std::atomic<int> g_prefill_kernel{0};
 
 // Tile shape: rows per CTA (128 or 256) and tokens per CTA (multiple of 32 up to 256), chosen
@@ -301,10 +301,10 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
     a.gpw = d.gpw; a.gshift = d.gshift;
     a.tile_m = 0;
     a.y_dtype = y_dtype;
-    // CTA pairs with the weight operand in tensor memory from 128 tokens on (below that the
-    // dequantization of a tile is most of its time in either kernel)
+    // CTA pairs with the weight operand in tensor memory unless the other kernel is asked for: the
+    // pair kernel is the faster one at every number of tokens measured (64 .. 4096)
     const int which = g_prefill_kernel.load(std::memory_order_relaxed);
-    if (which == 2 || (which == 0 && m >= 128)) {
+    if (which != 1) {
         const int rc = launch_dequant_gemm_pair(a, w->q, x, sms, stream);
         if (rc != HLQ_ERR_UNSUPPORTED) return rc;
     }

@@ -55,7 +55,7 @@ constexpr uint32_t kPairAccCols = 256, kPairACols = kPairStepK / 2;   // accumul
 constexpr uint32_t kPairTmemCols = 512;
 static_assert(kPairStages * kPairStepK == 512, "the ring of K steps is one slice of the streaming layout");
 static_assert(kPairAccCols + kPairStages * kPairACols <= kPairTmemCols, "tensor memory of one SM");
-static_assert(8 * (2 * kPairStages + 3) + 16 <= kBarBytes, "barriers");
+static_assert(8 * (2 * kPairStages + 4) + 16 <= kBarBytes, "barriers");
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -166,8 +166,8 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
     // CTA 0's producer) and one arrival per dequantizer warp that wrote its rows, so that the
     // issuing thread waits once per step.
     const uint32_t bar_full = bars, bar_empty = bars + 8 * kPairStages;
-    const uint32_t bar_acc = bars + 16 * kPairStages, bar_acc_empty = bar_acc + 8, bar_started = bar_acc + 16;
-    uint32_t *tmem_slot = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + kLutBytes + 16 * kPairStages + 24);
+    const uint32_t bar_acc = bars + 16 * kPairStages, bar_acc_empty = bar_acc + 8, bar_turn = bar_acc + 16;
+    uint32_t *tmem_slot = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + kLutBytes + 16 * kPairStages + 32);
     volatile int *fail = (volatile int *)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -184,7 +184,8 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_acc, 2);                                  // both issuing threads
-        mbar_init(bar_started, 1);
+        mbar_init(bar_turn, 1);
+        mbar_init(bar_turn + 8, 1);
         mbar_init(bar_acc_empty, 2 * kPairDeqWarps);            // every epilogue warp of both CTAs
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *fail = 0;
@@ -232,29 +233,28 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
         // ------------------------------ MMA issuers ---------------------------------------
         // Two threads of CTA 0 take the K steps in turn (warp 1 the even ones, warp 2 the odd ones):
         // the tensor cores take a product only when the one before has started, so a single thread
-        // spends a step's whole time issuing and the waits and commits between two steps leave
-        // the pipe idle; with two threads one waits and commits while the other issues.
+        // spends a step's whole time issuing, and its waits and commits between two steps leave
+        // the pipe idle; with two threads one waits and commits while the other issues.  They hand
+        // the turn to each other (bar_turn), so the products are issued in the order of the K steps
+        // and the sums come out the same in every run.
         if (lane == 0 && rank == 0) {
             const int who = warp - 1;
             const uint32_t idesc = pair_idesc(a.tile_m);
             const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_acc = map_to_cta(bar_acc, 1);
-            int it = 0;
+            int it = 0, mine = 0;                 // tiles; steps this thread has issued
             bool ok = true;
             for (int tile = pair; tile < ntiles && ok; tile += npairs, ++it) {
-                if (who == 0) {
-                    // the accumulator of the tile before has been read back by both CTAs
-                    if (it >= 1) ok = pair_wait(bar_acc_empty, (uint32_t)(it - 1) & 1u, fail);
-                } else {
-                    // the tile's first products (the ones that overwrite the accumulator) have been issued
-                    ok = pair_wait(bar_started, (uint32_t)it & 1u, fail);
-                }
+                // the accumulator of the tile before has been read back by both CTAs
+                if (who == 0 && it >= 1) ok = pair_wait(bar_acc_empty, (uint32_t)(it - 1) & 1u, fail);
                 if (!ok) break;
-                tc_fence_after();
-                for (int kt = who; kt < ksteps; kt += 2) {
+                for (int kt = who; kt < ksteps; kt += 2, ++mine) {
                     const int g = it * ksteps + kt;
                     const int s = g % kPairStages;
                     const uint32_t ph = (g / kPairStages) & 1;
                     ok = pair_wait(bar_full + 8 * s, ph, fail);
+                    // my turn: the other thread has issued the step before
+                    if (ok && (who == 1 || mine >= 1))
+                        ok = pair_wait(bar_turn + 8 * who, (uint32_t)(who == 1 ? mine : mine - 1) & 1u, fail);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t bdesc = umma_desc(tiles + s * kPairXStage);
@@ -263,10 +263,8 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                     for (int kk = 0; kk < kPairStepK / 16; ++kk)    // 16 channels = 8 columns of A, 32 bytes of B
                         umma_f16_ts_pair(tmem_base, acol + 8 * kk, bdesc + (uint64_t)((kk >> 2) * (kPairXBox >> 4) + 2 * (kk & 3)),
                                          idesc, (kt > 0 || kk > 0) ? 1u : 0u);
-                    if (kt == 0) {
-                        tc_fence_before();
-                        mbar_arrive(bar_started);
-                    }
+                    tc_fence_before();
+                    mbar_arrive(bar_turn + 8 * (who ^ 1));
                     umma_commit_pair(bar_empty + 8 * s);           // the stage is free again, in both CTAs
                     umma_commit_pair(peer_empty + 8 * s);
                 }
@@ -518,7 +516,7 @@ int pair_tile_tokens(int n, int m, int sms, double *cost) {
 }
 
 int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms, cudaStream_t stream) {
-    if (a_in.m < 64 || sms < 2) return HLQ_ERR_UNSUPPORTED;
+    if (a_in.m < 1 || sms < 2) return HLQ_ERR_UNSUPPORTED;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return HLQ_ERR_NO_DEVICE;
     GemmArgs a = a_in;

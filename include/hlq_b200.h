@@ -246,8 +246,8 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
 int hlq_select_batch_kernel(int which);
 
 /* Which kernel serves more than 16 rows of activations (for tests and measurements,
- * process-wide): 0 = the default (2 from 128 rows on, else 1), 1 = one CTA per tile of 256 (128)
- * weight rows, both operands in shared memory, 2 = a pair of CTAs per tile of 256 weight rows, the
+ * process-wide): 0 = the default (2), 1 = one CTA per tile of 256 (128) weight rows, both operands
+ * in shared memory, 2 = a pair of CTAs per tile of 256 weight rows, persistent over the tiles, the
  * dequantized weights in tensor memory, the token tile shared by the pair.  Same results up to
  * fp32 summation order. */
 int hlq_select_prefill_kernel(int which);

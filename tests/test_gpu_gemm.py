@@ -34,11 +34,22 @@ SHAPES = [
     (4, 64, 96, 32, 17, False),         # k smaller than one K step pair; fewest rows of x
     (1, 384, 2048, 128, 300, False),    # two token tiles
     (2, 1024, 5120, 64, 512, False),
+    (3, 600, 1024, 64, 200, True),      # three tiles of 256 rows, the last one ragged
+    (4, 520, 512, 128, 45, True),       # one slice; a tile of 64 tokens leaves half of the epilogue warps nothing
 ]
+KERNELS = [1, 2]                        # one CTA per tile, both operands in shared memory | CTA pairs, weights in tensor memory
+
+
+@pytest.fixture(params=KERNELS)
+def prefill_kernel(request, built_lib):
+    L = _lib.lib()
+    _lib.check(L.hlq_select_prefill_kernel(request.param), "hlq_select_prefill_kernel")
+    yield request.param
+    L.hlq_select_prefill_kernel(0)
 
 
 @pytest.mark.parametrize("q,n,k,g,m,bias", SHAPES)
-def test_gemm_matches_oracle(built_lib, q, n, k, g, m, bias):
+def test_gemm_matches_oracle(prefill_kernel, q, n, k, g, m, bias):
     if not torch.cuda.is_available():
         pytest.fail("needs a CUDA device")
     from elutq_b200 import linear as lm
@@ -53,6 +64,7 @@ def test_gemm_matches_oracle(built_lib, q, n, k, g, m, bias):
     assert O.normwise_error(y16.float().cpu().numpy(), ref) <= TOL
     # automatic dispatch: fp32 outputs go to this kernel above 16 rows, 16-bit outputs above 32
     # (below that two rows share every lookup of the LUT kernel, which is then faster)
+    # (the selected kernel stays selected: the choice is independent of the dispatch by rows)
     ya = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32)
     assert torch.equal(ya, y32)
     ya16 = lm.linear_forward(x, mod.weight, mod.workspace)
@@ -64,7 +76,7 @@ def test_gemm_matches_oracle(built_lib, q, n, k, g, m, bias):
         assert O.normwise_error(ya16.float().cpu().numpy(), ref) <= TOL
 
 
-def test_prefill_shape_of_the_13b_configuration(built_lib):
+def test_prefill_shape_of_the_13b_configuration(prefill_kernel):
     """Llama-2-13B projection at w2g64 with 2048 bf16 tokens; the oracle is evaluated on a
     random subset of output rows (the full float64 product would take minutes on the CPU)."""
     from elutq_b200 import linear as lm
@@ -85,7 +97,7 @@ def test_prefill_shape_of_the_13b_configuration(built_lib):
     assert torch.equal(y2, y * 2)
 
 
-def test_gemm_bf16_activations(built_lib):
+def test_gemm_bf16_activations(prefill_kernel):
     from elutq_b200 import linear as lm
     d, mod = build(2, 256, 1024, 64, 128, True, seed=77)
     xb = torch.from_numpy(d["x"].astype(np.float32)).cuda().bfloat16()
@@ -119,3 +131,30 @@ def test_gemm_rejects_exported_layout(built_lib):
     y = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32)     # generic kernel instead
     ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], 128)
     assert O.normwise_error(y.cpu().numpy(), ref) <= 1e-5
+
+
+def test_pair_kernel_walks_several_tiles_per_pair(built_lib):
+    """More tiles (10 x 8 = 80) than CTA pairs on the device (74 on a B200): some pairs run two
+    tiles, i.e. the ring of operand stages, the barrier phases and the hand-back of the
+    accumulator carry over a tile boundary.  bf16 outputs and a bias; oracle on a subset of rows;
+    the activations change between the two kernels so that neither can pass on the other's output."""
+    from elutq_b200 import linear as lm
+    L = _lib.lib()
+    n, k, q, g, m = 2560, 1024, 2, 64, 2048
+    d = O.synth_linear(n, k, q, g, m=m, seed=29, bias=True)
+    lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], d["bias"], g)
+    mod = lm.HLQLinear.from_exported(lin, device=0, max_batch=m)
+    rows = np.random.default_rng(1).choice(n, size=128, replace=False)
+    try:
+        for which, scale in ((2, 1.0), (1, 0.5)):
+            _lib.check(L.hlq_select_prefill_kernel(which), "hlq_select_prefill_kernel")
+            xh = (d["x"] * np.float16(scale)).astype(np.float16)
+            y = lm.linear_forward(torch.from_numpy(xh).cuda(), mod.weight, mod.workspace, out_dtype=torch.bfloat16,
+                                  impl=_lib.IMPL_GEMM)
+            torch.cuda.synchronize()
+            assert mod.workspace.kernel_status() == 0
+            ref = O.hlq_linear(xh, d["w_quant"][:, rows], d["w_scale"][:, rows], d["w_zero"][rows], g,
+                               d["bias"][rows], dtype=np.float64)
+            assert O.normwise_error(y[:, rows].float().cpu().numpy(), ref) <= TOL_BF16_OUT, which
+    finally:
+        L.hlq_select_prefill_kernel(0)
