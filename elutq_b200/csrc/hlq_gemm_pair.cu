@@ -6,23 +6,37 @@
 // the tensor cores read it back, which together with the nibble-table lookups keeps the
 // load/store pipe busier than the tensor pipe.  Here the weight operand never touches shared
 // memory, and two CTAs on neighbouring SMs (a cluster of two) share the token tile:
-//   * a pair owns 256 weight rows x up to 256 tokens; CTA c of the pair dequantizes rows
-//     128 c .. 128 c + 127 straight from registers into its own TENSOR MEMORY (tcgen05.st, one
-//     lane = one row, a column = two channels), eight K steps of 64 channels deep;
-//   * each CTA brings in HALF of the token tile of a K step by TMA (128-byte swizzle); the
-//     copies of both CTAs complete on the barrier of CTA 0 (cp.async.bulk.tensor ... cta_group::2);
-//   * one thread of CTA 0 issues tcgen05.mma.cta_group::2 (256 x tokens x 16, A from tensor memory
-//     of both SMs, B from shared memory of both SMs) and commits each stage free in both CTAs;
-//   * both CTAs read their 128 x tokens accumulator back and store y[token][row] (+ bias).
-// Shared memory carries 16 KB per K step and SM, a quarter of the single-CTA kernel's.
+//   * a pair owns tiles of 256 weight rows x up to 256 tokens and walks its share of them
+//     (persistent: tile = pair, pair + pairs, ...; tokens fastest, so a row tile's weights are hot
+//     in L2 for all its token tiles); CTA c of the pair dequantizes rows 128 c .. 128 c + 127
+//     straight from registers into its own TENSOR MEMORY (tcgen05.st, one lane = one row, a column
+//     = two channels), four K steps of 128 channels deep = one slice of the streaming layout;
+//   * each CTA brings in HALF of the token tile of a K step by TMA (two boxes of 64 channels,
+//     128-byte swizzle); the copies of both CTAs complete on a barrier of CTA 0
+//     (cp.async.bulk.tensor ... cta_group::2), the same barrier the dequantizer warps of both
+//     CTAs arrive on: one wait per K step tells the issuing thread that both operands are there;
+//   * threads of CTA 0 issue tcgen05.mma.cta_group::2 (256 x tokens x 16, A from tensor memory of
+//     both SMs, B from shared memory of both SMs) and commit each stage free in both CTAs;
+//   * both CTAs read their 128 x tokens accumulator back and store y[token][row] (+ bias); the
+//     stages and barrier phases run on across tiles, so while one tile is read back the first
+//     operands of the next are already in place and the tensor cores wait for the read-back only.
+// Shared memory carries 32 KB per K step of 128 channels and SM, a quarter of the single-CTA kernel's.
 //
 //   warp 0        TMA producer (one thread)
 //   warp 1        tensor memory allocation
 //   warps 1, 2    in CTA 0 one thread of each issues the products, K steps in turn
 //   warps 4..19   dequantizers, then epilogue: warp w owns lanes 32 (w & 3) .. +31 of tensor
 //                 memory (= rows of the tile) and quarter (w - 4) >> 2 of every slice of 512
-//                 channels, i.e. two of the eight K steps in flight: a lane's unit of work is
-//                 the streaming layout's unit, 16 bytes per plane = 128 channels of a row
+//                 channels = one of the four K steps in flight: a lane's unit of work is the
+//                 streaming layout's unit, 16 bytes per plane = 128 channels of a row
+//
+// Measured on a B200 (w2g64, 2048 tokens): 13824x5120 1.41 PFLOP/s, 5120x5120 1.10, 5120x13824 1.21
+// (dequant_gemm_kernel: 1.14, 0.72, 0.80); tensor pipe 75 % active.  What it was bound by on
+// the way, each found with cycle counters in the issuing thread and one dequantizer warp:
+// per-launch address arithmetic and 2-byte loads (a lane now loads 16 bytes per plane and slice),
+// two barrier waits and 64-channel steps (now one wait per 128 channels), a single issuing
+// thread whose waits and commits left the pipe idle (now two, alternating), tiles launched as
+// CTAs (now persistent).
 //
 // Precision and operand formats as in hlq_gemm.cu.  All waits are bounded (poll limit); the first
 // that runs out sets the CTA's failure flag, later waits give up at once, both CTAs still meet at
@@ -33,14 +47,6 @@
 
 namespace hlq {
 namespace gemm {
-
-#ifdef GP_TRACE
-__device__ long long g_trace_mma[8192];
-__device__ long long g_trace_deq[8192];
-#define GP_T(buf, idx) do { if (pair == 0 && (idx) < 8192) buf[idx] = clock64(); } while (0)
-#else
-#define GP_T(buf, idx) do { } while (0)
-#endif
 
 namespace {
 
@@ -386,7 +392,6 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                     }
                     if (nsl > 0 || tile + npairs < ntiles) load_slice<Q>(nxt, a, nsl, nn >> 3, 4 * (nn & 7) + part, nn < a.np);
                 }
-                if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs);
                 uint32_t src[Q][4];
 #pragma unroll
                 for (int p = 0; p < Q; ++p) source_words(cur.w[p], r, src[p]);
@@ -418,9 +423,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                     uint32_t o0[16], o1[16];
                     make(0, o0);
                     make(1, o1);
-                    if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 1);
                     if (gs >= 1) ok = pair_wait(bar_empty + 8 * s, (uint32_t)(gs - 1) & 1u, fail);
-                    if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 2);
                     if (!ok) break;
                     tc_fence_after();
                     put(0, o0);
@@ -437,9 +440,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(lead_full + 8 * s);
-                if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 3);
                 cur = nxt;
-                if (warp == 4 && lane == 0 && rank == 0) GP_T(g_trace_deq, 8 * gs + 7);
                 // the tile before: its accumulator is read back once this tile's first operands are on
                 // their way, so that the tensor cores wait for the read-back alone
                 if (sl == 0 && pending >= 0 && ok) {
@@ -542,11 +543,3 @@ int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms
 
 }  // namespace gemm
 }  // namespace hlq
-
-#ifdef GP_TRACE
-extern "C" int hlq_dbg_pair_trace(long long *mma, long long *deq) {
-    cudaMemcpyFromSymbol(mma, hlq::gemm::g_trace_mma, sizeof(long long) * 8192);
-    cudaMemcpyFromSymbol(deq, hlq::gemm::g_trace_deq, sizeof(long long) * 8192);
-    return 0;
-}
-#endif
