@@ -14,7 +14,7 @@ namespace gemm {
 constexpr int kTileK = 64;        // channels per K step: 128 bytes of 16-bit operands
 constexpr int kMaxTileM = 256;    // tokens per CTA at most (UMMA N)
 constexpr uint32_t kXBytes = kMaxTileM * kTileK * 2;   // 32 KB reserved per stage
-constexpr uint32_t kLutBytes = 256 * 16;
+constexpr uint32_t kLutBytes = 8192;        // nibble tables (256 bytes), byte tables of the pair kernel (4 KB)
 constexpr uint32_t kBarBytes = 256;
 constexpr int kSpinLimit = 1 << 24;
 

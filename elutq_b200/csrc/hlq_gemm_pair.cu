@@ -50,6 +50,7 @@ namespace gemm {
 
 namespace {
 
+constexpr uint32_t kByteTableBytes = 4096;                      // byte tables of two- and three-plane weights
 constexpr int kPairStepK = 128;                                  // channels per K step: a quarter of a slice
 constexpr int kPairStages = 4;                                   // K steps in flight (both operands): one slice
 constexpr int kPairDeqWarps = 16;
@@ -59,6 +60,7 @@ constexpr uint32_t kPairXStage = 2 * kPairXBox;                  // two boxes: 1
 constexpr uint32_t kPairDynSmem = 1024 + kPairStages * kPairXStage + kLutBytes + kBarBytes;
 constexpr uint32_t kPairAccCols = 256, kPairACols = kPairStepK / 2;   // accumulator; one K step of the weight operand
 constexpr uint32_t kPairTmemCols = 512;
+static_assert(256 + kByteTableBytes <= kLutBytes, "tables");
 static_assert(kPairStages * kPairStepK == 512, "the ring of K steps is one slice of the streaming layout");
 static_assert(kPairAccCols + kPairStages * kPairACols <= kPairTmemCols, "tensor memory of one SM");
 static_assert(8 * (2 * kPairStages + 4) + 16 <= kBarBytes, "barriers");
@@ -116,6 +118,107 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_mbar) {
                  : "memory");
 }
 
+// ---- two- and three-plane weights: a byte of a plane (8 channels) is looked up whole --------------
+// Two planes: entry b of table p is, for the 8 channels of plane byte b, one selector byte per
+// channel (.x channels 0..3, .y channels 4..7): 0x10 + 0x22 bit for plane 0, 0x44 bit for plane 1;
+// the OR of the two entries selects, per pair of channels, the fp16 values z + b0 a0 + b1 a1 out of
+// the 8 bytes {v0, v1, v2, v3} with one prmt.
+// Three planes: entry b of table p is the byte's 8 bits spread to bit p of 8 nibbles; the OR of the
+// three entries is the 3-bit code of 8 channels, which indexes byte tables of the 8 possible values
+// (their low bytes in two registers, their high bytes in two): two prmt gather 4 low and 4 high
+// bytes, two more pair them up.
+// Either way a weight costs about half the ALU instructions of the nibble-mask form and the 2^q
+// values of a group are rounded to fp16 once, from fp32.
+template <int Q>
+__device__ __forceinline__ void fill_byte_tables(int tid, int nthreads, unsigned char *tab) {
+    if constexpr (Q == 2) {
+        uint2 *t = (uint2 *)tab;                       // [plane][256]
+        for (int e = tid; e < 512; e += nthreads) {
+            const int p = e >> 8, b = e & 255;
+            const uint32_t unit = p == 0 ? 0x22u : 0x44u, base = p == 0 ? 0x10101010u : 0u;
+            uint32_t lo = base, hi = base;
+            for (int c = 0; c < 4; ++c) {
+                if (b >> c & 1) lo += unit << (8 * c);
+                if (b >> (4 + c) & 1) hi += unit << (8 * c);
+            }
+            t[e] = make_uint2(lo, hi);
+        }
+    } else if constexpr (Q == 3) {
+        uint32_t *t = (uint32_t *)tab;                 // [plane][256]
+        for (int e = tid; e < 768; e += nthreads) {
+            const int p = e >> 8, b = e & 255;
+            uint32_t w = 0u;
+            for (int c = 0; c < 8; ++c)
+                if (b >> c & 1) w |= 1u << (4 * c + p);
+            t[e] = w;
+        }
+    }
+}
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+// the values a weight of one group can take, as prmt sources
+template <int Q>
+struct GroupValues {
+    uint32_t v[Q == 2 ? 2 : 4];      // q = 2: {v0, v1}, {v2, v3} as fp16 pairs; q = 3: low bytes x2, high bytes x2
+};
+template <int Q>
+__device__ __forceinline__ void group_values(GroupValues<Q> &gv, const uint16_t (&alpha)[Q], uint16_t zero) {
+    float val[1 << Q];
+    val[0] = __half2float(__ushort_as_half(zero));
+#pragma unroll
+    for (int p = 0; p < Q; ++p) {
+        const float ap = __half2float(__ushort_as_half(alpha[p]));
+#pragma unroll
+        for (int e = 0; e < (1 << p); ++e) val[(1 << p) + e] = val[e] + ap;
+    }
+    uint32_t pr[(1 << Q) / 2];
+#pragma unroll
+    for (int e = 0; e < (1 << Q) / 2; ++e) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(pr[e]) : "f"(val[2 * e + 1]), "f"(val[2 * e]));
+    if constexpr (Q == 2) {
+        gv.v[0] = pr[0];
+        gv.v[1] = pr[1];
+    } else {
+        gv.v[0] = prmt_b32(pr[0], pr[1], 0x6420u);     // low bytes of values 0..3
+        gv.v[1] = prmt_b32(pr[2], pr[3], 0x6420u);     // 4..7
+        gv.v[2] = prmt_b32(pr[0], pr[1], 0x7531u);     // high bytes of values 0..3
+        gv.v[3] = prmt_b32(pr[2], pr[3], 0x7531u);     // 4..7
+    }
+}
+// 32 channels (bits[p] = the 32 bits of plane p in channel order) as 16 fp16 pairs
+template <int Q>
+__device__ __forceinline__ void expand32(const uint32_t (&bits)[Q], const GroupValues<Q> &gv, const unsigned char *tab,
+                                         uint32_t (&o)[16]) {
+    if constexpr (Q == 2) {
+        const uint2 *t = (const uint2 *)tab;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint2 e0 = t[(bits[0] >> (8 * k)) & 0xffu], e1 = t[256 + ((bits[1] >> (8 * k)) & 0xffu)];
+            const uint32_t sx = e0.x | e1.x, sy = e0.y | e1.y;
+            o[4 * k] = prmt_b32(gv.v[0], gv.v[1], sx);
+            o[4 * k + 1] = prmt_b32(gv.v[0], gv.v[1], sx >> 16);
+            o[4 * k + 2] = prmt_b32(gv.v[0], gv.v[1], sy);
+            o[4 * k + 3] = prmt_b32(gv.v[0], gv.v[1], sy >> 16);
+        }
+    } else {
+        const uint32_t *t = (const uint32_t *)tab;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t code = t[(bits[0] >> (8 * k)) & 0xffu] | t[256 + ((bits[1] >> (8 * k)) & 0xffu)] |
+                                  t[512 + ((bits[2] >> (8 * k)) & 0xffu)];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t sel = h ? code >> 16 : code;
+                const uint32_t lb = prmt_b32(gv.v[0], gv.v[1], sel), hb = prmt_b32(gv.v[2], gv.v[3], sel);
+                o[4 * k + 2 * h] = prmt_b32(lb, hb, 0x5140u);
+                o[4 * k + 2 * h + 1] = prmt_b32(lb, hb, 0x7362u);
+            }
+        }
+    }
+}
+
 // What a dequantizer thread fetches for one slice of 512 channels: the 16 bytes per plane that hold
 // the 128 channels of its row in its quarter of the slice, and the fp16 scales / zero of the
 // (up to four) groups they fall into, low bits first.
@@ -166,6 +269,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
     const uint32_t lut_u32 = tiles + kPairStages * kPairXStage;
     uint2 *lut = (uint2 *)(tiles_ptr + kPairStages * kPairXStage);
     uint32_t *sel_lut = (uint32_t *)(tiles_ptr + kPairStages * kPairXStage + 128);   // 2 x 16 words
+    const unsigned char *byte_tab = tiles_ptr + kPairStages * kPairXStage + 256;   // kByteTableBytes
     const uint32_t bars = lut_u32 + kLutBytes;
     // barriers: full[s] and acc_empty (waited for in CTA 0 only), empty[s], acc_full; TMEM base; flag.
     // full[s] counts both operands of a K step: the token tile's bytes of both CTAs (announced by
@@ -197,6 +301,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
         *fail = 0;
     }
     if (tid < 16) fill_dequant_tables(tid, lut, sel_lut);
+    if constexpr (Q == 2 || Q == 3) fill_byte_tables<Q>(tid, kPairThreads, tiles_ptr + kPairStages * kPairXStage + 256);
     if (warp == 1) {   // all of tensor memory, in both CTAs with one instruction each
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(kPairTmemCols) : "memory");
@@ -399,17 +504,28 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                 // weights are made before the wait for the stage (it is busy for as long as the products
                 // that read it, and the arithmetic need not wait for them), the other half after.
                 const int s = part;
+                GroupValues<(Q == 2 || Q == 3) ? Q : 2> gv;
                 auto make = [&](int ws, uint32_t (&o)[16]) {                  // 32 channels of the lane's 128
                     const int u = ((ws * a.gpw) >> 2) ^ gsel;
                     uint32_t bits[Q];
-                    uint16_t al[Q];
 #pragma unroll
-                    for (int p = 0; p < Q; ++p) {
-                        bits[p] = src[p][ws];
-                        al[p] = (uint16_t)((((uint64_t)cur.mt[p].y << 32 | cur.mt[p].x) >> (16 * u)) & 0xffffu);
+                    for (int p = 0; p < Q; ++p) bits[p] = src[p][ws];
+                    // scales and zero of the group: anew only where the group changes (g = 128: once
+                    // per slice, g = 64: twice, g = 32: for every 32 channels)
+                    const bool fresh = ws == 0 || a.gpw == 4 || (a.gpw == 2 && ws == 2);
+                    uint16_t al[Q], z = 0;
+                    if (fresh || !(Q == 2 || Q == 3)) {
+#pragma unroll
+                        for (int p = 0; p < Q; ++p)
+                            al[p] = (uint16_t)((((uint64_t)cur.mt[p].y << 32 | cur.mt[p].x) >> (16 * u)) & 0xffffu);
+                        z = (uint16_t)((((uint64_t)cur.mt[Q].y << 32 | cur.mt[Q].x) >> (16 * u)) & 0xffffu);
                     }
-                    const uint16_t z = (uint16_t)((((uint64_t)cur.mt[Q].y << 32 | cur.mt[Q].x) >> (16 * u)) & 0xffffu);
-                    dequant_channels<Q, 32>(bits, al, z, lut, sel_lut, o);
+                    if constexpr (Q == 2 || Q == 3) {
+                        if (fresh) group_values<Q>(gv, al, z);
+                        expand32<Q>(bits, gv, byte_tab, o);
+                    } else {
+                        dequant_channels<Q, 32>(bits, al, z, lut, sel_lut, o);
+                    }
                 };
                 auto put = [&](int ws, const uint32_t (&o)[16]) {
                     asm volatile(
