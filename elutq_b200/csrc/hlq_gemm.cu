@@ -300,6 +300,7 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
     a.m = m; a.n = w->n; a.k = w->k; a.np = d.np; a.kp = d.kp; a.octs = d.octs; a.duos = d.duos;
     a.gpw = d.gpw; a.gshift = d.gshift;
     a.tile_m = 0;
+    a.tok_group = 1;
     a.y_dtype = y_dtype;
     // CTA pairs with the weight operand in tensor memory unless the other kernel is asked for: the
     // pair kernel is the faster one at every number of tokens measured (64 .. 4096)

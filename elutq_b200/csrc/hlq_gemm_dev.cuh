@@ -26,6 +26,7 @@ struct GemmArgs {
     int *status;
     int m, n, k, np, kp, octs, duos, gpw, gshift;
     int tile_m;          // tokens per CTA: multiple of 32, <= 256
+    int tok_group;       // pair kernel: token tiles walked together (their activations share L2)
     int y_dtype;
 };
 

@@ -7,8 +7,8 @@
 // load/store pipe busier than the tensor pipe.  Here the weight operand never touches shared
 // memory, and two CTAs on neighbouring SMs (a cluster of two) share the token tile:
 //   * a pair owns tiles of 256 weight rows x up to 256 tokens and walks its share of them
-//     (persistent: tile = pair, pair + pairs, ...; tokens fastest, so a row tile's weights are hot
-//     in L2 for all its token tiles); CTA c of the pair dequantizes rows 128 c .. 128 c + 127
+//     (persistent: tile = pair, pair + pairs, ...; token tiles in groups that fit L2, inside a group
+//     a row tile's token tiles one after the other); CTA c of the pair dequantizes rows 128 c .. 128 c + 127
 //     straight from registers into its own TENSOR MEMORY (tcgen05.st, one lane = one row, a column
 //     = two channels), four K steps of 128 channels deep = one slice of the streaming layout;
 //   * each CTA brings in HALF of the token tile of a K step by TMA (two boxes of 64 channels,
@@ -286,7 +286,23 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
     const int half_m = a.tile_m >> 1;                         // tokens this CTA brings in
     const int ksteps = a.kp / kPairStepK;                     // a multiple of 4: the streaming layout pads K to 512
     const int tok_tiles = (a.m + a.tile_m - 1) / a.tile_m;
-    const int ntiles = ((a.n + 255) / 256) * tok_tiles;       // tile = (256 rows) x (tile_m tokens), tokens fastest
+    const int row_tiles = (a.n + 255) / 256;
+    const int ntiles = row_tiles * tok_tiles;
+    // Order of the tiles = (256 rows) x (tile_m tokens): the token tiles go in groups of a.tok_group
+    // whose activations stay in L2 together; inside a group the row tiles in turn, and for a row
+    // tile the group's token tiles one after the other (so its packed weights come from HBM once
+    // per group, and the activations once per group instead of once per row tile).
+    const int group_tiles = row_tiles * a.tok_group;
+    auto row_tile_of = [&](int tile) {
+        const int grp = tile / group_tiles, rem = tile - grp * group_tiles;
+        const int width = min(a.tok_group, tok_tiles - grp * a.tok_group);
+        return rem / width;
+    };
+    auto tok_tile_of = [&](int tile) {
+        const int grp = tile / group_tiles, rem = tile - grp * group_tiles;
+        const int width = min(a.tok_group, tok_tiles - grp * a.tok_group);
+        return grp * a.tok_group + rem % width;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < kPairStages; ++s) {
@@ -327,7 +343,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
             int g = 0;
             bool ok = true;
             for (int tile = pair; tile < ntiles && ok; tile += npairs) {
-                const int m0 = (tile % tok_tiles) * a.tile_m;
+                const int m0 = tok_tile_of(tile) * a.tile_m;
                 for (int kt = 0; kt < ksteps; ++kt, ++g) {
                     const int s = g % kPairStages;
                     if (g >= kPairStages) ok = pair_wait(bar_empty + 8 * s, ((g / kPairStages) - 1) & 1, fail);
@@ -395,8 +411,8 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
 
         // the accumulator of a finished tile: read back, + bias, stored as y[token][row]
         auto epilogue = [&](int tile, uint32_t parity) {
-            const int row = (tile / tok_tiles) * 256 + 128 * (int)rank + t;
-            const int m0 = (tile % tok_tiles) * a.tile_m;
+            const int row = row_tile_of(tile) * 256 + 128 * (int)rank + t;
+            const int m0 = tok_tile_of(tile) * a.tile_m;
             pair_wait(bar_acc, parity, fail);
             tc_fence_after();
             float bv = 0.f;
@@ -479,7 +495,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
         };
 
         RawSlice<Q> cur, nxt;
-        int n = (pair / tok_tiles) * 256 + 128 * (int)rank + t;
+        int n = (pair < ntiles ? row_tile_of(pair) : 0) * 256 + 128 * (int)rank + t;
         if (pair < ntiles) load_slice<Q>(cur, a, 0, n >> 3, 4 * (n & 7) + part, n < a.np);
         int gs = 0, it = 0;                      // slices and tiles so far
         int pending = -1;                        // tile whose accumulator is still to be read back
@@ -493,7 +509,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                     int nn = n, nsl = sl + 1;
                     if (nsl == slices) {
                         nsl = 0;
-                        nn = ((tile + npairs) / tok_tiles) * 256 + 128 * (int)rank + t;
+                        nn = (tile + npairs < ntiles ? row_tile_of(tile + npairs) : 0) * 256 + 128 * (int)rank + t;
                     }
                     if (nsl > 0 || tile + npairs < ntiles) load_slice<Q>(nxt, a, nsl, nn >> 3, 4 * (nn & 7) + part, nn < a.np);
                 }
@@ -565,7 +581,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                 }
             }
             pending = tile;
-            n = ((tile + npairs) / tok_tiles) * 256 + 128 * (int)rank + t;
+            n = (tile + npairs < ntiles ? row_tile_of(tile + npairs) : 0) * 256 + 128 * (int)rank + t;
         }
         if (pending >= 0) epilogue(pending, (uint32_t)(it - 1) & 1u);
     }
@@ -638,6 +654,13 @@ int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms
     if (!enc) return HLQ_ERR_NO_DEVICE;
     GemmArgs a = a_in;
     a.tile_m = pair_tile_tokens(a.n, a.m, sms, nullptr);
+    {
+        // token tiles whose activations (tile_m x k fp16 each) fit a third of a B200's L2 together
+        const long long tile_bytes = (long long)a.tile_m * a.k * 2, budget = 40ll << 20;
+        const int tok_tiles = (a.m + a.tile_m - 1) / a.tile_m;
+        long long g = budget / (tile_bytes > 0 ? tile_bytes : 1);
+        a.tok_group = (int)(g < 1 ? 1 : (g > tok_tiles ? tok_tiles : g));
+    }
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};

@@ -158,3 +158,26 @@ def test_pair_kernel_walks_several_tiles_per_pair(built_lib):
             assert O.normwise_error(y[:, rows].float().cpu().numpy(), ref) <= TOL_BF16_OUT, which
     finally:
         L.hlq_select_prefill_kernel(0)
+
+
+def test_pair_kernel_with_more_tokens_than_stay_in_l2(built_lib):
+    """2048 tokens x 10240 channels are 42 MB of activations: the pair kernel walks the token tiles
+    in groups (here 7 + 1, the last group narrower than the others).  Oracle on a subset of rows."""
+    from elutq_b200 import linear as lm
+    L = _lib.lib()
+    n, k, q, g, m = 512, 10240, 2, 128, 2048
+    d = O.synth_linear(n, k, q, g, m=m, seed=31, bias=True)
+    lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], d["bias"], g)
+    mod = lm.HLQLinear.from_exported(lin, device=0, max_batch=m)
+    rows = np.random.default_rng(2).choice(n, size=64, replace=False)
+    try:
+        _lib.check(L.hlq_select_prefill_kernel(2), "hlq_select_prefill_kernel")
+        y = lm.linear_forward(torch.from_numpy(d["x"]).cuda(), mod.weight, mod.workspace, out_dtype=torch.float32,
+                              impl=_lib.IMPL_GEMM)
+        torch.cuda.synchronize()
+        assert mod.workspace.kernel_status() == 0
+        ref = O.hlq_linear(d["x"], d["w_quant"][:, rows], d["w_scale"][:, rows], d["w_zero"][rows], g,
+                           d["bias"][rows], dtype=np.float64)
+        assert O.normwise_error(y[:, rows].cpu().numpy(), ref) <= TOL
+    finally:
+        L.hlq_select_prefill_kernel(0)
