@@ -29,6 +29,17 @@ def test_status_strings(built_lib):
     assert b"unknown" in built_lib.hlq_last_error_string(99)
 
 
+def test_kernel_selectors_check_their_argument(built_lib):
+    """The process-wide kernel selectors (for tests and measurements) take 0 .. their last kernel
+    and refuse anything else without changing the selection."""
+    for fn, last in ((built_lib.hlq_select_batch_kernel, 3), (built_lib.hlq_select_prefill_kernel, 2)):
+        for which in range(last + 1):
+            assert fn(which) == 0
+        assert fn(0) == 0
+        for bad in (-1, last + 1, 99):
+            assert fn(bad) == 1          # HLQ_ERR_INVALID_ARGUMENT
+
+
 def test_pack_matches_reference_bytes(built_lib):
     d = np.load(f"{GOLDEN}/pack_q4_n16_k64.npz")
     assert np.array_equal(F.pack_bits(d["planes"]), d["packed"])
