@@ -276,10 +276,10 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
     if (!enc) return HLQ_ERR_NO_DEVICE;
     const StreamDims d = stream_dims(w->n, w->k, w->g, w->q);
     if (x_dtype == HLQ_BF16) {
-        // fp16 copy of the activations behind the workspace header
-        const size_t bytes = (size_t)m * w->k * 2;
-        if (workspace_bytes < kWsHeader + bytes) return HLQ_ERR_WORKSPACE;
-        void *x16 = (char *)workspace + kWsHeader;
+        // fp16 copy of the activations, behind what the LUT kernels keep in the workspace
+        const size_t bytes = (size_t)m * w->k * 2, off = gemm_scratch_offset(d);
+        if (workspace_bytes < off + bytes) return HLQ_ERR_WORKSPACE;
+        void *x16 = (char *)workspace + off;
         const int64_t nvec = (int64_t)(bytes / 16);       // k % 8 == 0
         int64_t blocks = (nvec + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;

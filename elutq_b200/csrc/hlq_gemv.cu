@@ -709,14 +709,14 @@ static size_t lut_scratch_bytes(int m, const StreamDims &d) {
     return kWsHeader + counters + partial;
 }
 
+// Where the tensor-core GEMM may put its fp16 copy of bf16 activations: behind everything a LUT
+// launch of any number of rows keeps in the workspace (counters and accumulators that are zero
+// between calls), so that one workspace serves prefill and decode calls in any order.
+size_t gemm_scratch_offset(const StreamDims &d) { return (lut_scratch_bytes(kLutMaxM, d) + 255) / 256 * 256; }
+
 size_t workspace_bytes_for(int m, const StreamDims &d) {
     size_t need = lut_scratch_bytes(m, d);
-    // more rows than the GEMV takes go to the tensor-core GEMM, which may need an fp16 copy
-    // of bf16 activations
-    if (m > kLutMaxM) {
-        const size_t gemm = kWsHeader + (size_t)m * d.k * 2;
-        if (gemm > need) need = gemm;
-    }
+    if (m > kLutMaxM) need = gemm_scratch_offset(d) + (size_t)m * d.k * 2;
     return need;
 }
 

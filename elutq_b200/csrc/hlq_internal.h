@@ -90,6 +90,7 @@ struct Workspace {
     float *partial;      // [m][np] fp32 accumulators
 };
 size_t workspace_bytes_for(int m, const StreamDims &d);
+size_t gemm_scratch_offset(const StreamDims &d);   // byte offset of the GEMM's fp16 copy of bf16 activations
 Workspace carve_workspace(void *base, int m, const StreamDims &d);
 
 // Kernels' launchers (defined in the .cu files).  All return an hlq_status.

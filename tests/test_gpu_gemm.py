@@ -181,3 +181,22 @@ def test_pair_kernel_with_more_tokens_than_stay_in_l2(built_lib):
         assert O.normwise_error(y[:, rows].cpu().numpy(), ref) <= TOL
     finally:
         L.hlq_select_prefill_kernel(0)
+
+
+def test_one_workspace_serves_prefill_and_decode_calls_in_any_order(built_lib):
+    """A prefill call with bf16 tokens puts their fp16 copy into the workspace; the LUT kernels
+    keep counters and accumulators there that must be zero between calls.  The two must not share
+    bytes: decode-sized calls after a prefill call (and the other way round) stay correct."""
+    from elutq_b200 import linear as lm
+    d = O.synth_linear(512, 1024, 2, 128, m=64, seed=3, bias=True)
+    lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], d["bias"], 128)
+    mod = lm.HLQLinear.from_exported(lin, device=0, max_batch=64)
+    xb = torch.from_numpy(d["x"].astype(np.float32)).cuda().bfloat16()
+    ref = O.hlq_linear(xb.float().cpu().numpy(), d["w_quant"], d["w_scale"], d["w_zero"], 128, d["bias"])
+    for _ in range(2):
+        y = lm.linear_forward(xb, mod.weight, mod.workspace, out_dtype=torch.float32)
+        assert O.normwise_error(y.cpu().numpy(), ref) <= TOL
+        for m in (1, 2, 4, 16, 24):
+            ym = lm.linear_forward(xb[:m], mod.weight, mod.workspace, out_dtype=torch.float16)
+            assert O.normwise_error(ym.float().cpu().numpy(), ref[:m]) <= TOL, m
+            assert mod.workspace.kernel_status() == 0
