@@ -412,13 +412,11 @@ int hlq_linear_forward_impl(int impl, int m, int k, int n, const void *d_x, int 
     HLQ_CUDA(cudaGetDevice(&cur));
     if (cur != w->device) return HLQ_ERR_INVALID_ARGUMENT;
     if (impl == 0) {
-        // exported layout -> generic kernel; few rows -> LUT GEMV; more -> dequantize +
-        // tensor-core GEMM.  The GEMM costs about the same for any m below ~256 (it is bound by
-        // the dequantization: 0.45 ms for a Llama-2-13B layer), a LUT pass of two rows 23 us on
-        // the same layer, so with 16-bit outputs (paired rows) the LUT path wins up to 32 rows;
-        // fp32 outputs (one row per pass) change over at 16.
+        // exported layout -> generic kernel; up to 16 rows -> the LUT GEMV and the small-batch
+        // kernel; more -> dequantize + tensor-core GEMM (measured on a Llama-3-8B layer at w3g128:
+        // 32 rows as two launches of 16 take 289 us, the GEMM 140 us for any m up to 128).
         if (w->layout == HLQ_LAYOUT_EXPORT) impl = 2;
-        else impl = (m <= kLutMaxM || (m <= 2 * kLutMaxM && y_dtype != HLQ_F32)) ? 1 : 3;
+        else impl = m <= kLutMaxM ? 1 : 3;
     }
     int rc;
     switch (impl) {

@@ -301,12 +301,17 @@ int launch_dequant_gemm(const hlq_weight *w, int m, const void *x, int x_dtype, 
     a.gpw = d.gpw; a.gshift = d.gshift;
     a.tile_m = 0;
     a.tok_group = 1;
+    a.ksplit = 1;
+    a.acc = nullptr;
     a.y_dtype = y_dtype;
     // CTA pairs with the weight operand in tensor memory unless the other kernel is asked for: the
     // pair kernel is the faster one at every number of tokens measured (64 .. 4096)
     const int which = g_prefill_kernel.load(std::memory_order_relaxed);
     if (which != 1) {
-        const int rc = launch_dequant_gemm_pair(a, w->q, x, sms, stream);
+        // fp32 sums of a K split (few tokens and few rows): behind the fp16 copy of the tokens
+        const size_t acc_off = gemm_acc_offset(m, d);
+        float *acc = workspace_bytes > acc_off ? (float *)((char *)workspace + acc_off) : nullptr;
+        const int rc = launch_dequant_gemm_pair(a, w->q, x, sms, acc, acc ? workspace_bytes - acc_off : 0, stream);
         if (rc != HLQ_ERR_UNSUPPORTED) return rc;
     }
     int rows = 128, tile_m = 256;

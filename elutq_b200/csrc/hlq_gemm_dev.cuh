@@ -27,6 +27,8 @@ struct GemmArgs {
     int m, n, k, np, kp, octs, duos, gpw, gshift;
     int tile_m;          // tokens per CTA: multiple of 32, <= 256
     int tok_group;       // pair kernel: token tiles walked together (their activations share L2)
+    int ksplit;          // pair kernel: parts K is split into (1: outputs are stored; > 1: sums go to acc)
+    float *acc;          // pair kernel, ksplit > 1: ksplit fp32 slabs [m][n] in the workspace
     int y_dtype;
 };
 
@@ -209,7 +211,10 @@ inline EncodeTiledFn encode_fn() {
 
 // The same problem on CTA pairs (hlq_gemm_pair.cu); `x` is fp16.  HLQ_ERR_UNSUPPORTED: use the
 // single-CTA kernel.
-int launch_dequant_gemm_pair(const GemmArgs &a, int q, const void *x, int sms, cudaStream_t stream);
+// `acc`: room for fp32 slabs [m][n] in the workspace, one per part of a split K (nullptr or fewer than
+// two slabs: K is not split).
+int launch_dequant_gemm_pair(const GemmArgs &a, int q, const void *x, int sms, float *acc, size_t acc_bytes,
+                             cudaStream_t stream);
 // tokens per pair tile and (optionally) waves x tokens as a cost to compare tilings by
 int pair_tile_tokens(int n, int m, int sms, double *cost);
 

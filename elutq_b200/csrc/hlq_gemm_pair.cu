@@ -298,6 +298,14 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
         const int width = min(a.tok_group, tok_tiles - grp * a.tok_group);
         return rem / width;
     };
+    // Few tiles (few tokens, few rows): K is split S ways so that all pairs have work.  A unit is
+    // (tile, part of K) = S consecutive unit numbers per tile; its sums go to slab number `part`
+    // of S fp32 slabs [m][n] in the workspace (a.acc), which a small kernel adds up and finishes.
+    const int S = a.ksplit, slices_total = ksteps >> 2;
+    const int nunits = ntiles * S;
+    auto unit_tile = [&](int u) { return u / S; };
+    auto unit_s0 = [&](int u) { return slices_total * (u % S) / S; };
+    auto unit_s1 = [&](int u) { return slices_total * (u % S + 1) / S; };
     auto tok_tile_of = [&](int tile) {
         const int grp = tile / group_tiles, rem = tile - grp * group_tiles;
         const int width = min(a.tok_group, tok_tiles - grp * a.tok_group);
@@ -342,9 +350,9 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
             const uint32_t xbytes = (uint32_t)a.tile_m * kPairStepK * 2;  // both halves, both boxes
             int g = 0;
             bool ok = true;
-            for (int tile = pair; tile < ntiles && ok; tile += npairs) {
-                const int m0 = tok_tile_of(tile) * a.tile_m;
-                for (int kt = 0; kt < ksteps; ++kt, ++g) {
+            for (int u = pair; u < nunits && ok; u += npairs) {
+                const int m0 = tok_tile_of(unit_tile(u)) * a.tile_m;
+                for (int kt = 4 * unit_s0(u); kt < 4 * unit_s1(u); ++kt, ++g) {
                     const int s = g % kPairStages;
                     if (g >= kPairStages) ok = pair_wait(bar_empty + 8 * s, ((g / kPairStages) - 1) & 1, fail);
                     if (!ok) break;
@@ -368,14 +376,15 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
             const int who = warp - 1;
             const uint32_t idesc = pair_idesc(a.tile_m);
             const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_acc = map_to_cta(bar_acc, 1);
-            int it = 0, mine = 0;                 // tiles; steps this thread has issued
+            int it = 0, mine = 0, g0 = 0;         // units; steps this thread has issued; steps of the units before
             bool ok = true;
-            for (int tile = pair; tile < ntiles && ok; tile += npairs, ++it) {
+            for (int u = pair; u < nunits && ok; u += npairs, ++it) {
+                const int kt0 = 4 * unit_s0(u), kt1 = 4 * unit_s1(u);
                 // the accumulator of the tile before has been read back by both CTAs
                 if (who == 0 && it >= 1) ok = pair_wait(bar_acc_empty, (uint32_t)(it - 1) & 1u, fail);
                 if (!ok) break;
-                for (int kt = who; kt < ksteps; kt += 2, ++mine) {
-                    const int g = it * ksteps + kt;
+                for (int kt = kt0 + who; kt < kt1; kt += 2, ++mine) {
+                    const int g = g0 + kt - kt0;
                     const int s = g % kPairStages;
                     const uint32_t ph = (g / kPairStages) & 1;
                     ok = pair_wait(bar_full + 8 * s, ph, fail);
@@ -389,7 +398,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
 #pragma unroll
                     for (int kk = 0; kk < kPairStepK / 16; ++kk)    // 16 channels = 8 columns of A, 32 bytes of B
                         umma_f16_ts_pair(tmem_base, acol + 8 * kk, bdesc + (uint64_t)((kk >> 2) * (kPairXBox >> 4) + 2 * (kk & 3)),
-                                         idesc, (kt > 0 || kk > 0) ? 1u : 0u);
+                                         idesc, (kt > kt0 || kk > 0) ? 1u : 0u);
                     tc_fence_before();
                     mbar_arrive(bar_turn + 8 * (who ^ 1));
                     umma_commit_pair(bar_empty + 8 * s);           // the stage is free again, in both CTAs
@@ -398,6 +407,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                 // also after a wait that gave up: the products issued so far end, both CTAs' epilogues wake
                 umma_commit_pair(bar_acc);
                 umma_commit_pair(peer_acc);
+                g0 += kt1 - kt0;
             }
         }
     } else if (warp >= 4) {
@@ -407,10 +417,10 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
         const int part = wd >> 2;                // quarter of every slice = K step `part` of its four = stage `part`
         const int t = 32 * q4 + lane;            // weight row inside this CTA's half of the tile
         const uint32_t tlane = tmem_base + ((uint32_t)(32 * q4) << 16);
-        const int slices = ksteps >> 2;
 
         // the accumulator of a finished tile: read back, + bias, stored as y[token][row]
-        auto epilogue = [&](int tile, uint32_t parity) {
+        auto epilogue = [&](int unit, uint32_t parity) {
+            const int tile = unit_tile(unit), ks = unit % S;
             const int row = row_tile_of(tile) * 256 + 128 * (int)rank + t;
             const int m0 = tok_tile_of(tile) * a.tile_m;
             pair_wait(bar_acc, parity, fail);
@@ -449,7 +459,8 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                     if (tok < a.m) {
                         const float o = __uint_as_float(v[c]) + bv;
                         const int64_t idx = (int64_t)tok * a.n + row;
-                        if (a.y_dtype == HLQ_F16) ((__half *)a.y)[idx] = __float2half_rn(o);
+                        if (S > 1) a.acc[(int64_t)ks * a.m * a.n + idx] = __uint_as_float(v[c]);   // this part's slab; the finishing kernel adds them up
+                        else if (a.y_dtype == HLQ_F16) ((__half *)a.y)[idx] = __float2half_rn(o);
                         else if (a.y_dtype == HLQ_BF16) ((__nv_bfloat16 *)a.y)[idx] = __float2bfloat16_rn(o);
                         else ((float *)a.y)[idx] = o;
                     }
@@ -461,7 +472,7 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                 load32(c00);
                 release();
                 if (good) store32(c00);
-            } else if (a.y_dtype == HLQ_F32) {           // two chunks of fp32 outputs: no room to keep the first
+            } else if (a.y_dtype == HLQ_F32 || S > 1) {  // two chunks of fp32 values: no room to keep the first
                 load32(c00);
                 if (good) store32(c00);
                 load32(c01);
@@ -495,23 +506,25 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
         };
 
         RawSlice<Q> cur, nxt;
-        int n = (pair < ntiles ? row_tile_of(pair) : 0) * 256 + 128 * (int)rank + t;
-        if (pair < ntiles) load_slice<Q>(cur, a, 0, n >> 3, 4 * (n & 7) + part, n < a.np);
-        int gs = 0, it = 0;                      // slices and tiles so far
-        int pending = -1;                        // tile whose accumulator is still to be read back
+        auto row_of_unit = [&](int u) { return (u < nunits ? row_tile_of(unit_tile(u)) : 0) * 256 + 128 * (int)rank + t; };
+        int n = row_of_unit(pair);
+        if (pair < nunits) load_slice<Q>(cur, a, unit_s0(pair), n >> 3, 4 * (n & 7) + part, n < a.np);
+        int gs = 0, it = 0;                      // slices and units so far
+        int pending = -1;                        // unit whose accumulator is still to be read back
         bool ok = true;
-        for (int tile = pair; tile < ntiles && ok; tile += npairs, ++it) {
+        for (int u = pair; u < nunits && ok; u += npairs, ++it) {
             const int r = n & 7;
             const int gsel = r >> a.gshift;      // stored group u holds source group u ^ gsel
-            for (int sl = 0; sl < slices && ok; ++sl, ++gs) {
-                // the next slice of this tile, else the first slice of the next tile
+            const int sl0 = unit_s0(u), sl1 = unit_s1(u);
+            for (int sl = sl0; sl < sl1 && ok; ++sl, ++gs) {
+                // the next slice of this unit, else the first slice of the next unit
                 {
                     int nn = n, nsl = sl + 1;
-                    if (nsl == slices) {
-                        nsl = 0;
-                        nn = (tile + npairs < ntiles ? row_tile_of(tile + npairs) : 0) * 256 + 128 * (int)rank + t;
+                    if (nsl == sl1) {
+                        nsl = u + npairs < nunits ? unit_s0(u + npairs) : 0;
+                        nn = row_of_unit(u + npairs);
                     }
-                    if (nsl > 0 || tile + npairs < ntiles) load_slice<Q>(nxt, a, nsl, nn >> 3, 4 * (nn & 7) + part, nn < a.np);
+                    if (sl + 1 < sl1 || u + npairs < nunits) load_slice<Q>(nxt, a, nsl, nn >> 3, 4 * (nn & 7) + part, nn < a.np);
                 }
                 uint32_t src[Q][4];
 #pragma unroll
@@ -575,13 +588,13 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
                 cur = nxt;
                 // the tile before: its accumulator is read back once this tile's first operands are on
                 // their way, so that the tensor cores wait for the read-back alone
-                if (sl == 0 && pending >= 0 && ok) {
+                if (sl == sl0 && pending >= 0 && ok) {
                     epilogue(pending, (uint32_t)(it - 1) & 1u);
                     pending = -1;
                 }
             }
-            pending = tile;
-            n = (tile + npairs < ntiles ? row_tile_of(tile + npairs) : 0) * 256 + 128 * (int)rank + t;
+            pending = u;
+            n = row_of_unit(u + npairs);
         }
         if (pending >= 0) epilogue(pending, (uint32_t)(it - 1) & 1u);
     }
@@ -596,8 +609,41 @@ dequant_gemm_pair_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap x
     if (tid == 0 && *fail) atomicExch(a.status, 1);
 }
 
+// Finishes a launch whose K was split: y = sum of the parts' slabs (+ bias) in the output type.
+// The parts are added in their order, so the result is the same in every run.
+__global__ void pair_finish_kernel(const float *__restrict__ acc, void *__restrict__ y, const uint16_t *__restrict__ bias,
+                                   long long total, int n, int parts, int y_dtype) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        float o = 0.f;
+        for (int p = 0; p < parts; ++p) o += __ldcs(acc + (long long)p * total + i);
+        if (bias) o += __half2float(__ushort_as_half(bias[i % n]));
+        if (y_dtype == HLQ_F16) ((__half *)y)[i] = __float2half_rn(o);
+        else if (y_dtype == HLQ_BF16) ((__nv_bfloat16 *)y)[i] = __float2bfloat16_rn(o);
+        else ((float *)y)[i] = o;
+    }
+}
+
+// How many parts to split K into, by a cost in microseconds fitted to measurements on a B200: a
+// slice of 512 channels takes a pair about 1.8, a unit's first operands and its read-back 8, the
+// finishing kernel 4 plus its reads at 4 bytes per part and output.  At most max_parts slabs fit.
+int choose_ksplit(int ntiles, int slices, int pairs, long long outputs, int max_parts) {
+    int best_s = 1;
+    double best = -1.0;
+    for (int sp = 1; sp <= slices && sp <= max_parts && sp <= 16; ++sp) {
+        const long long rounds = ((long long)ntiles * sp + pairs - 1) / pairs;
+        const double unit = 1.8 * ((slices + sp - 1) / sp) + 8.0;
+        const double cost = rounds * unit + (sp > 1 ? 4.0 + 4.0e-6 * sp * outputs / 4.0 : 0.0);
+        if (best < 0 || cost < best * 0.97) {      // a split must win clearly
+            best = cost;
+            best_s = sp;
+        }
+    }
+    return best_s;
+}
+
 template <int Q>
-int launch_pair_inst(const GemmArgs &a, const CUtensorMap &xmap, int ntiles, cudaStream_t stream) {
+int launch_pair_inst(GemmArgs &a, const CUtensorMap &xmap, int ntiles, size_t acc_bytes, cudaStream_t stream) {
     static int pairs_cached[64] = {};        // clusters of two that run at once, per device; 0 = not asked yet
     int dev = 0;
     HLQ_CUDA(cudaGetDevice(&dev));
@@ -621,8 +667,20 @@ int launch_pair_inst(const GemmArgs &a, const CUtensorMap &xmap, int ntiles, cud
         if (nclusters < 1) return HLQ_ERR_UNSUPPORTED;
         pairs = nclusters;
     }
-    const int use = ntiles < pairs ? ntiles : pairs;
+    // few tiles: split K, if the workspace has room for the fp32 sums
+    a.ksplit = 1;
+    const long long total = (long long)a.m * a.n;
+    if (ntiles < pairs && a.acc && acc_bytes >= 2 * (size_t)total * sizeof(float))
+        a.ksplit = choose_ksplit(ntiles, a.kp / 512, pairs, total, (int)(acc_bytes / ((size_t)total * sizeof(float))));
+    const int nunits = ntiles * a.ksplit;
+    const int use = nunits < pairs ? nunits : pairs;
     kernel<<<2 * use, kPairThreads, kPairDynSmem, stream>>>(a, xmap);
+    count_launch();
+    int rc = note_cuda(cudaGetLastError());
+    if (rc || a.ksplit == 1) return rc;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    pair_finish_kernel<<<(int)blocks, 256, 0, stream>>>(a.acc, a.y, a.bias, total, a.n, a.ksplit, a.y_dtype);
     count_launch();
     return note_cuda(cudaGetLastError());
 }
@@ -648,11 +706,13 @@ int pair_tile_tokens(int n, int m, int sms, double *cost) {
     return tile;
 }
 
-int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms, cudaStream_t stream) {
+int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms, float *acc, size_t acc_bytes,
+                             cudaStream_t stream) {
     if (a_in.m < 1 || sms < 2) return HLQ_ERR_UNSUPPORTED;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return HLQ_ERR_NO_DEVICE;
     GemmArgs a = a_in;
+    a.acc = acc;
     a.tile_m = pair_tile_tokens(a.n, a.m, sms, nullptr);
     {
         // token tiles whose activations (tile_m x k fp16 each) fit a third of a B200's L2 together
@@ -672,10 +732,10 @@ int launch_dequant_gemm_pair(const GemmArgs &a_in, int q, const void *x, int sms
         return HLQ_ERR_INVALID_ARGUMENT;
     const int ntiles = ((a.n + 255) / 256) * ((a.m + a.tile_m - 1) / a.tile_m);
     switch (q) {
-        case 1: return launch_pair_inst<1>(a, xmap, ntiles, stream);
-        case 2: return launch_pair_inst<2>(a, xmap, ntiles, stream);
-        case 3: return launch_pair_inst<3>(a, xmap, ntiles, stream);
-        case 4: return launch_pair_inst<4>(a, xmap, ntiles, stream);
+        case 1: return launch_pair_inst<1>(a, xmap, ntiles, acc_bytes, stream);
+        case 2: return launch_pair_inst<2>(a, xmap, ntiles, acc_bytes, stream);
+        case 3: return launch_pair_inst<3>(a, xmap, ntiles, acc_bytes, stream);
+        case 4: return launch_pair_inst<4>(a, xmap, ntiles, acc_bytes, stream);
     }
     return HLQ_ERR_SHAPE;
 }

@@ -714,9 +714,21 @@ static size_t lut_scratch_bytes(int m, const StreamDims &d) {
 // between calls), so that one workspace serves prefill and decode calls in any order.
 size_t gemm_scratch_offset(const StreamDims &d) { return (lut_scratch_bytes(kLutMaxM, d) + 255) / 256 * 256; }
 
+// ... and behind that copy the fp32 slabs [m][n] of a GEMM whose K is split (at most kGemmSplitMaxM rows of x).
+size_t gemm_acc_offset(int m, const StreamDims &d) {
+    return gemm_scratch_offset(d) + ((size_t)m * d.k * 2 + 255) / 256 * 256;
+}
+
 size_t workspace_bytes_for(int m, const StreamDims &d) {
     size_t need = lut_scratch_bytes(m, d);
-    if (m > kLutMaxM) need = gemm_scratch_offset(d) + (size_t)m * d.k * 2;
+    if (m > kLutMaxM) {
+        need = gemm_acc_offset(m, d);
+        // slabs for a split K: only problems of fewer tiles (256 rows each) than a B200 has SM pairs split
+        if (m <= kGemmSplitMaxM && (d.n + 255) / 256 < 74) {
+            const size_t slab = (size_t)m * d.n * sizeof(float);
+            need += 8 * slab < kGemmSlabBytes ? 8 * slab : kGemmSlabBytes;
+        }
+    }
     return need;
 }
 

@@ -202,7 +202,12 @@ int hlq_weight_build_batch_codes(hlq_weight *w, void *stream);
 /* ---- forward ------------------------------------------------------------------------ */
 
 /* Bytes of device scratch hlq_linear_forward needs for this problem (0 is possible).
- * Replaces the temp_workplace sizing of C++/ops/src/arm/arm_gemm.cpp:333-334,348. */
+ * Replaces the temp_workplace sizing of C++/ops/src/arm/arm_gemm.cpp:333-334,348.
+ * A workspace sized for m rows serves every call with at most m rows, in any order: the regions
+ * of the kernels do not overlap (status word; counters and fp32 accumulators of the 1..16-row
+ * kernels, zero between calls; above 16 rows an fp16 copy of bf16 activations and, up to 256
+ * rows, fp32 slabs [m][n] for problems that are split along K).  After a call that ended with
+ * HLQ_ERR_KERNEL zero the workspace again (hlq_workspace_init). */
 size_t hlq_workspace_bytes(int m, int k, int n, int bits, int groupsize);
 /* Zero a freshly allocated workspace once, before its first use (the forward kernels
  * leave it in the state they need).  One workspace serves one stream at a time. */
