@@ -93,7 +93,7 @@ size_t workspace_bytes_for(int m, const StreamDims &d);
 size_t gemm_scratch_offset(const StreamDims &d);   // byte offset of the GEMM's fp16 copy of bf16 activations
 size_t gemm_acc_offset(int m, const StreamDims &d); // ... and of its fp32 sums when K is split
 constexpr int kGemmSplitMaxM = 256;                // rows of x up to which the workspace holds room for them
-constexpr size_t kGemmSlabBytes = 32u << 20;       // ... at most this much (up to 8 slabs)
+constexpr size_t kGemmSlabBytes = 16u << 20;       // ... at most this much (up to 8 slabs)
 Workspace carve_workspace(void *base, int m, const StreamDims &d);
 
 // Kernels' launchers (defined in the .cu files).  All return an hlq_status.
