@@ -195,3 +195,35 @@ def test_one_workspace_serves_prefill_and_decode_calls_in_any_order(built_lib):
             ym = lm.linear_forward(xb[:m], mod.weight, mod.workspace, out_dtype=torch.float16)
             assert O.normwise_error(ym.float().cpu().numpy(), ref[:m]) <= TOL, m
             assert mod.workspace.kernel_status() == 0
+
+
+@pytest.mark.parametrize("m", [17, 48, 256])
+def test_pair_kernel_splits_a_long_k_over_the_pairs(built_lib, m):
+    """Two tiles of 256 rows and 16 slices of K: the pair kernel splits K into as many parts as
+    its slabs allow (8) and a finishing kernel adds them up.  Every output type, with a bias; two
+    calls give the same bits (the parts are added in order)."""
+    from elutq_b200 import linear as lm
+    L = _lib.lib()
+    n, k, q, g = 512, 8192, 2, 128
+    d = O.synth_linear(n, k, q, g, m=m, seed=41 + m, bias=True, signed_alpha=True)
+    lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], d["bias"], g)
+    mod = lm.HLQLinear.from_exported(lin, device=0, max_batch=m)
+    ref = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
+    x = torch.from_numpy(d["x"]).cuda()
+    try:
+        _lib.check(L.hlq_select_prefill_kernel(2), "hlq_select_prefill_kernel")
+        for dt, tol in ((torch.float32, TOL), (torch.float16, TOL), (torch.bfloat16, TOL_BF16_OUT)):
+            y = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=dt)
+            y2 = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=dt)
+            torch.cuda.synchronize()
+            assert mod.workspace.kernel_status() == 0
+            assert O.normwise_error(y.float().cpu().numpy(), ref) <= tol, dt
+            assert torch.equal(y, y2)
+        # the same product without the split (the other kernel) agrees to fp32 summation order
+        _lib.check(L.hlq_select_prefill_kernel(1), "hlq_select_prefill_kernel")
+        y1 = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32, impl=_lib.IMPL_GEMM)
+        _lib.check(L.hlq_select_prefill_kernel(2), "hlq_select_prefill_kernel")
+        y = lm.linear_forward(x, mod.weight, mod.workspace, out_dtype=torch.float32)
+        assert O.normwise_error(y.cpu().numpy(), y1.cpu().numpy()) <= 1e-4
+    finally:
+        L.hlq_select_prefill_kernel(0)
