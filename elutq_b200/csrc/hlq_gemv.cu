@@ -723,9 +723,11 @@ size_t workspace_bytes_for(int m, const StreamDims &d) {
     size_t need = lut_scratch_bytes(m, d);
     if (m > kLutMaxM) {
         need = gemm_acc_offset(m, d);
-        // slabs for a split K: only problems of fewer tiles (256 rows each) than a B200 has SM pairs split
-        if (m <= kGemmSplitMaxM && (d.n + 255) / 256 < 74) {
-            const size_t slab = (size_t)m * d.n * sizeof(float);
+        // slabs for a split K: only problems of fewer tiles (256 rows each) than a B200 has SM pairs
+        // split, and only calls of at most kGemmSplitMaxM rows; counted for every m above 16 so that
+        // the size grows with m (a workspace for m rows serves every call with fewer)
+        if ((d.n + 255) / 256 < 74) {
+            const size_t slab = (size_t)(m < kGemmSplitMaxM ? m : kGemmSplitMaxM) * d.n * sizeof(float);
             need += 8 * slab < kGemmSlabBytes ? 8 * slab : kGemmSlabBytes;
         }
     }

@@ -227,3 +227,31 @@ def test_pair_kernel_splits_a_long_k_over_the_pairs(built_lib, m):
         assert O.normwise_error(y.cpu().numpy(), y1.cpu().numpy()) <= 1e-4
     finally:
         L.hlq_select_prefill_kernel(0)
+
+
+@pytest.mark.parametrize("q,g", [(2, 64), (3, 128)])
+def test_random_sequence_of_calls_on_one_workspace(built_lib, q, g):
+    """Forty calls with 1..300 rows, fp16 or bf16 inputs and every output type, in a seeded random
+    order on ONE weight and ONE workspace: every kernel family (LUT passes, the small-batch
+    kernel, the pair kernel with and without a split K) leaves the workspace as the next one
+    needs it."""
+    from elutq_b200 import linear as lm
+    n, k, mmax = 640, 2048, 300
+    d = O.synth_linear(n, k, q, g, m=mmax, seed=7 * q + g, bias=True, signed_alpha=True)
+    lin = F.ExportedLinear(d["w_quant"], d["w_scale"], d["w_zero"], d["bias"], g)
+    mod = lm.HLQLinear.from_exported(lin, device=0, max_batch=mmax)
+    x16 = torch.from_numpy(d["x"]).cuda()
+    xb = x16.float().bfloat16()
+    ref16 = O.hlq_linear(d["x"], d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
+    refb = O.hlq_linear(xb.float().cpu().numpy(), d["w_quant"], d["w_scale"], d["w_zero"], g, d["bias"])
+    rng = np.random.default_rng(99)
+    rows = [1, 2, 3, 5, 8, 13, 16, 17, 24, 32, 33, 64, 100, 128, 129, 256, 257, 300]
+    for step in range(40):
+        m = int(rng.choice(rows))
+        bf = bool(rng.integers(0, 2))
+        dt = [torch.float32, torch.float16, torch.bfloat16][int(rng.integers(0, 3))]
+        y = lm.linear_forward((xb if bf else x16)[:m], mod.weight, mod.workspace, out_dtype=dt)
+        torch.cuda.synchronize()
+        assert mod.workspace.kernel_status() == 0, (step, m)
+        tol = TOL_BF16_OUT if dt == torch.bfloat16 else TOL
+        assert O.normwise_error(y.float().cpu().numpy(), (refb if bf else ref16)[:m]) <= tol, (step, m, bf, dt)

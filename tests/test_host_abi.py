@@ -40,6 +40,17 @@ def test_kernel_selectors_check_their_argument(built_lib):
             assert fn(bad) == 1          # HLQ_ERR_INVALID_ARGUMENT
 
 
+def test_workspace_size_grows_with_the_rows(built_lib):
+    """A workspace sized for m rows serves every call with at most m rows: the size never shrinks
+    as m grows (also across the row counts at which another kernel takes over)."""
+    for (k, n, q, g) in [(2048, 640, 2, 64), (4096, 4096, 3, 128), (8192, 28672, 2, 128), (512, 128, 4, 32)]:
+        prev = 0
+        for m in range(1, 600):
+            b = built_lib.hlq_workspace_bytes(m, k, n, q, g)
+            assert b >= prev, (m, k, n, q, g)
+            prev = b
+
+
 def test_pack_matches_reference_bytes(built_lib):
     d = np.load(f"{GOLDEN}/pack_q4_n16_k64.npz")
     assert np.array_equal(F.pack_bits(d["planes"]), d["packed"])
