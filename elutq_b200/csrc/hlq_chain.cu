@@ -57,7 +57,7 @@ constexpr int kChBarConsumers = 1;   // 512 consumer threads
 constexpr int kChBarItemDone = 2;    // +slot: consumers arrive, finalizers sync (640)
 constexpr int kChBarFinalizers = 6;  // 128 finalizer threads
 
-enum { CH_IN_PLAIN = 0, CH_IN_NORM = 1, CH_IN_ATTENTION = 2 };
+enum { CH_IN_PLAIN = 0, CH_IN_NORM = 1, CH_IN_ATTENTION = 2, CH_IN_GATED_ACC = 3 };   // the last one is set by the host, not by callers
 enum { CH_OUT_STORE = 0, CH_OUT_RESIDUAL = 1, CH_OUT_GATED_SILU = 2 };
 enum { CH_STAGE_GEMV = 0, CH_STAGE_ATTENTION = 1 };
 enum { CH_ITEM_END = 0, CH_ITEM_SEGMENT = 1, CH_ITEM_ATTENTION = 2, CH_ITEM_NOTHING = 3 };
@@ -135,7 +135,13 @@ struct __align__(16) ChainItem {
     unsigned dep_target;     // done[stage - 1] when the stage before this one is complete
     int job_first, stage_jobs;   // the stage's linears (stage_jobs = 0: not a GEMV stage)
     unsigned stage_blocks;   // blocks of 32 rows of all the stage's linears = done[stage] when complete
-    int pad_[5];
+    // A GEMV stage whose only input is the gated-SiLU output of the single linear of the stage before
+    // (down after gate/up) skips that stage's completion pass: its consumers read the fp32 sums
+    // themselves (x = those accumulators, gamma = that linear's bias, attn_ml = its fp16 output, which
+    // they still write), gated by raw[] instead of done[]; the stage before only counts its CTAs
+    // (defer_out), and this stage's completion pass clears the accumulators it read (clear_acc).
+    int dep_raw, defer_out, clear_blocks;
+    float *clear_acc;
 };
 
 // aux region layout (bytes from its start)
@@ -252,7 +258,7 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
     int d = 0, dend = 0;
 
     int cur_kind = CH_ITEM_END;
-    bool cur_norm = false, cur_attn = false;
+    bool cur_norm = false, cur_attn = false, cur_gated = false;
     // first loads of an item (its descriptor stays in its ring slot until the consumers hand
     // the item over, so only what the streaming loop needs is kept in registers)
     auto open_item = [&](const ChainItem &it) {
@@ -260,6 +266,7 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
         if (it.kind != CH_ITEM_SEGMENT) return;
         cur_norm = it.in_kind == CH_IN_NORM;
         cur_attn = it.in_kind == CH_IN_ATTENTION;
+        cur_gated = it.in_kind == CH_IN_GATED_ACC;
         d = it.duo_a + warp;
         dend = it.duo_b;
         pl = it.planes + (long long)warp * kDuoPlaneBytes + lane * 16;
@@ -297,6 +304,31 @@ __device__ __forceinline__ bool chain_gemv_items(const ChainArgs &a, unsigned ch
                 xw[tid] = __half_as_ushort(__float2half_rn(val));
                 named_bar_sync<kChBarConsumers, kChConsumers>();
                 if (tid == 0) stamp(i, 15);
+            }
+            if (cur_gated) {
+                // the activations are the gated SiLU of the stage before, whose fp32 sums are complete
+                // (raw[] gate) but not finished: one channel per thread, the roundings of the
+                // completion pass (fp16 gate, fp16 up, fp16 product); rows 32 b .. + 15 are gate rows,
+                // + 16 .. + 31 the up rows of channels 16 b .. + 15
+                const ChainItem &it = CH_RING[slot];
+                const float *sums = (const float *)it.x;
+                uint16_t *xw = (uint16_t *)(aux + kChAuxX) + slot * kSliceK;
+                uint16_t hb = 0;
+                if (tid < it.valid) {
+                    const int c = it.slice * kSliceK + tid;
+                    const int row = 32 * (c >> 4) + (c & 15);
+                    float gate = ldcg_f32(sums + row), up = ldcg_f32(sums + row + 16);
+                    if (it.gamma) {
+                        gate += __half2float(__ushort_as_half(it.gamma[row]));
+                        up += __half2float(__ushort_as_half(it.gamma[row + 16]));
+                    }
+                    const float mine = __half2float(__float2half_rn(gate)), other = __half2float(__float2half_rn(up));
+                    const __half h = __float2half_rn(other * (mine / (1.0f + expf(-mine))));
+                    hb = __half_as_ushort(h);
+                    ((__half *)it.attn_ml)[c] = h;       // the stage's output stays where callers expect it
+                }
+                xw[tid] = hb;
+                named_bar_sync<kChBarConsumers, kChConsumers>();
             }
             const bool norm = cur_norm;
             const float inv_rms = norm ? ((const float *)(aux + kChAuxInvRms))[slot] : 1.f;
@@ -480,7 +512,7 @@ __global__ void __launch_bounds__(kChThreads, 1) decode_chain_kernel(const __gri
         // releases the inputs of the item in `slot` to the consumers (control warp)
         auto release = [&](int slot) {
             const ChainItem &it = ring[slot];
-            if (it.kind == CH_ITEM_SEGMENT && it.in_kind != CH_IN_ATTENTION && !*fail) {
+            if (it.kind == CH_ITEM_SEGMENT && it.in_kind != CH_IN_ATTENTION && it.in_kind != CH_IN_GATED_ACC && !*fail) {
                 const bool norm = it.in_kind == CH_IN_NORM;
                 uint16_t *xs = (uint16_t *)(aux + kChAuxX) + slot * kSliceK;
                 uint16_t *gs = (uint16_t *)(aux + kChAuxGamma) + slot * kSliceK;
@@ -510,14 +542,16 @@ __global__ void __launch_bounds__(kChThreads, 1) decode_chain_kernel(const __gri
             __syncwarp();
         };
         // waits (bounded) until the stage that gates `stage` is complete (control warp)
-        auto wait_dep = [&](int dep, unsigned target) {
+        auto wait_dep = [&](int dep, unsigned target, bool on_raw) {
             if (dep < 0 || dep <= known_done) return;
             int ok = 0;
+            const unsigned *counter = on_raw ? a.raw + dep : a.done + dep;     // CTAs that streamed, or finished blocks
+            if (on_raw) target = gridDim.x;
             if (lane == 0 && !*fail) {           // the lane that polls is the lane that issues the copies
                 const unsigned long long t0 = global_ns();
                 for (;;) {
 #pragma unroll 1
-                    for (int k = 0; k < 16 && !ok; ++k) ok = ld_acquire_gpu_u32(a.done + dep) >= target;
+                    for (int k = 0; k < 16 && !ok; ++k) ok = ld_acquire_gpu_u32(counter) >= target;
                     if (ok || *fail || ld_relaxed_gpu_s32(a.status) != 0 || global_ns() - t0 > budget) break;
                 }
             }
@@ -558,7 +592,7 @@ __global__ void __launch_bounds__(kChThreads, 1) decode_chain_kernel(const __gri
                 const int dep = it.stage - 1;
                 const bool gated = it.kind != CH_ITEM_NOTHING && dep > known_done;
                 if (gated && issued > done_upto + 1) break;
-                if (gated) wait_dep(dep, it.dep_target);
+                if (gated) wait_dep(dep, it.dep_target, it.dep_raw != 0);
                 if (lane == 0) stamp(issued, 0);
                 release(ps);
                 if (lane == 0) stamp(issued, 1);
@@ -587,7 +621,13 @@ __global__ void __launch_bounds__(kChThreads, 1) decode_chain_kernel(const __gri
             // of ALL CTAs: read the accumulators, run the linear's output op (or push the sums to the
             // ranks and add theirs), clear the accumulators; 4. fence, add the number of finished
             // blocks to done[stage].  Which CTA streamed last no longer matters for who completes what.
-            if (it.last_of_stage && it.stage_jobs > 0) {
+            if (it.last_of_stage && it.stage_jobs > 0 && it.defer_out) {
+                // the next stage's consumers finish this stage's sums themselves: count this CTA, no more
+                if (ftid == 0 && !*fail) {
+                    __threadfence();
+                    atomicAdd(a.raw + it.stage, 1u);
+                }
+            } else if (it.last_of_stage && it.stage_jobs > 0) {
                 if (ftid == 0 && !*fail) {
                     __threadfence();
                     atomicAdd(a.raw + it.stage, 1u);
@@ -611,6 +651,10 @@ __global__ void __launch_bounds__(kChThreads, 1) decode_chain_kernel(const __gri
                 const bool push = tp && it.tp_ordinal > 0;
                 const unsigned tag = tag_base + (unsigned)it.tp_ordinal;
                 const int nwarps = gridDim.x * kChFinalWarps, wme = blockIdx.x * kChFinalWarps + fw;
+                // every CTA has streamed this stage, so every CTA has read the sums of the stage before
+                // that this one took unfinished: they are cleared here, for the next token
+                if (it.clear_acc && !failed)
+                    for (int blk = wme; blk < it.clear_blocks; blk += nwarps) it.clear_acc[blk * kBlockRows + lane] = 0.f;
                 int ndone = 0;
                 int off = 0;                               // blocks of the jobs before this one
                 for (int jj = 0; jj < it.stage_jobs && !failed; ++jj) {
@@ -985,10 +1029,29 @@ static void chain_build_items(const hlq_chain *c, int ctas, int q, int gpw, std:
         const ChainStage &st = c->stages[si];
         std::vector<size_t> before(ctas);
         for (int g = 0; g < ctas; ++g) before[g] = out[g].size();
+        // Stage t hands its sums to stage t + 1 unfinished when it is ONE linear with gated-SiLU output
+        // and no rank sum, and stage t + 1 is ONE linear that takes exactly that output as plain input.
+        auto hands_over = [&](size_t t) {
+            if (t + 1 >= c->stages.size()) return false;
+            const ChainStage &sa = c->stages[t], &sb = c->stages[t + 1];
+            if (sa.kind != CH_STAGE_GEMV || sb.kind != CH_STAGE_GEMV || sa.job_count != 1 || sb.job_count != 1) return false;
+            if (sa.tp_ordinal != 0) return false;
+            const ChainJob &ja = c->jobs[sa.job_begin], &jb = c->jobs[sb.job_begin];
+            return ja.out_kind == CH_OUT_GATED_SILU && jb.in_kind == CH_IN_PLAIN && (const void *)jb.x == (const void *)ja.y &&
+                   jb.k * 2 == ja.n;
+        };
+        const bool takes_sums = si >= 1 && hands_over(si - 1), gives_sums = hands_over(si);
         auto base_item = [&](int kind) {
             ChainItem it = {};
             it.kind = kind;
             it.stage = (int)si;
+            it.defer_out = gives_sums ? 1 : 0;
+            if (takes_sums) {
+                const ChainJob &ja = c->jobs[c->stages[si - 1].job_begin];
+                it.dep_raw = 1;
+                it.clear_acc = ja.acc;
+                it.clear_blocks = ja.blocks;
+            }
             it.tp_ordinal = st.tp_ordinal;
             it.dep_target = prev_target;
             it.job_index = st.kind == CH_STAGE_GEMV ? st.job_begin : -1;
@@ -1033,6 +1096,13 @@ static void chain_build_items(const hlq_chain *c, int ctas, int q, int gpw, std:
                 it.attn_ml = jb.in_kind == HLQ_CHAIN_IN_ATTENTION
                                  ? (const float *)jb.x + (size_t)jb.attn_heads * jb.attn_nsplit * 128 : nullptr;
                 it.valid = jb.k - p.slice * kSliceK < kSliceK ? jb.k - p.slice * kSliceK : kSliceK;
+                if (takes_sums) {
+                    const ChainJob &ja = c->jobs[c->stages[si - 1].job_begin];
+                    it.in_kind = CH_IN_GATED_ACC;
+                    it.x = (const uint16_t *)ja.acc;
+                    it.gamma = ja.bias;
+                    it.attn_ml = (const float *)ja.y;
+                }
                 return it;
             };
             const int np = (int)pairs.size();
