@@ -149,3 +149,50 @@ def test_chain_against_the_decoder_oracle(tmp_path):
         want, hidden = ora.step(tok, pos)
         got = dec.last_logits.float().cpu().numpy()[0].astype(np.float64)
         assert np.abs(got - want).max() / np.abs(want).max() <= 1e-2, pos
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("q,g,hidden,ffn,n_out", [(2, 128, 1024, 640, 768), (3, 64, 512, 1536, 520)])
+def test_down_takes_the_gate_up_sums_unfinished(q, g, hidden, ffn, n_out):
+    """A chain of two linears, fused gate/up (with a bias, gated-SiLU output) and a down projection
+    that takes exactly that output: the kernel skips gate/up's completion pass, down's consumers
+    finish the sums themselves (ffn = 640: the second slice of down holds 128 channels) and
+    down's completion pass clears them.  The intermediate output and the result against NumPy with
+    the kernel's roundings, three tokens in a row (the sums are zero again each time)."""
+    if not torch.cuda.is_available():
+        pytest.fail("needs a CUDA device")
+    from elutq_b200 import _lib, format as F
+    from elutq_b200.chain import DecodeChain, interleave_rows
+    from elutq_b200.linear import HLQWeight
+    from oracle import hlq_oracle as O
+    dev = torch.device("cuda", 0)
+    dg = O.synth_linear(ffn, hidden, q, g, m=1, seed=51, bias=True, signed_alpha=True)
+    du = O.synth_linear(ffn, hidden, q, g, m=1, seed=52, bias=True, signed_alpha=True)
+    dd = O.synth_linear(n_out, ffn, q, g, m=1, seed=53, bias=True, signed_alpha=True)
+    fused = F.ExportedLinear(interleave_rows(dg["w_quant"], du["w_quant"], 1), interleave_rows(dg["w_scale"], du["w_scale"], 1),
+                             interleave_rows(dg["w_zero"], du["w_zero"], 0), interleave_rows(dg["bias"], du["bias"], 0), g)
+    wgu = HLQWeight.from_export(fused, device=0)
+    wd = HLQWeight.from_export(F.ExportedLinear(dd["w_quant"], dd["w_scale"], dd["w_zero"], dd["bias"], g), device=0)
+    x = torch.zeros(hidden, dtype=torch.float16, device=dev)
+    h = torch.zeros(ffn, dtype=torch.float16, device=dev)
+    y = torch.zeros(n_out, dtype=torch.float16, device=dev)
+    chain = DecodeChain(dev, 0)
+    chain.add_linears([DecodeChain.linear(wgu, x, h, out_kind=_lib.HLQ_CHAIN_OUT_GATED_SILU)])
+    chain.add_linears([DecodeChain.linear(wd, h, y)])
+    chain.finish()
+    rng = np.random.default_rng(5)
+    for step in range(3):
+        xs = rng.standard_normal(hidden).astype(np.float16)
+        x.copy_(torch.from_numpy(xs))
+        h.zero_()
+        y.zero_()
+        chain.forward()
+        torch.cuda.synchronize()
+        assert chain.status() == 0
+        gate = O.hlq_linear(xs[None], dg["w_quant"], dg["w_scale"], dg["w_zero"], g, dg["bias"])[0].astype(np.float16).astype(np.float32)
+        up = O.hlq_linear(xs[None], du["w_quant"], du["w_scale"], du["w_zero"], g, du["bias"])[0].astype(np.float16).astype(np.float32)
+        href = (up * (gate / (1.0 + np.exp(-gate)))).astype(np.float16)
+        hk = h.cpu().numpy()
+        assert O.normwise_error(hk.astype(np.float64), href.astype(np.float64)) <= 2e-3, step
+        yref = O.hlq_linear(hk[None], dd["w_quant"], dd["w_scale"], dd["w_zero"], g, dd["bias"])[0]
+        assert O.normwise_error(y.float().cpu().numpy().astype(np.float64), yref) <= 1e-3, step
